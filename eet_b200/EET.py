@@ -1,0 +1,544 @@
+"""Drop-in for the int8 weight-only part of the reference's pybind11 module ``EET``
+(csrc/py11/eet2py.cpp:17-156): the same class and function names, argument order and meaning, backed
+by the sm_100a kernels of libeet_b200.so through ctypes.
+
+    import eet_b200.EET as EET            # or eet_b200.install_as_EET(); then `from EET import ...`
+    from eet_b200.EET import MetaDesc, LlamaMmha, BaichuanMmha, GatedFeedForwardNetworkInt8, LayerNorm
+    from eet_b200.EET import quant_weights, preprocess_weights
+
+Covered: MetaDesc, LlamaMmha, BaichuanMmha, GatedFeedForwardNetworkInt8, LayerNorm (RMSNorm form),
+quant_weights, preprocess_weights - everything python/eet/transformers/modeling_llama.py and
+modeling_baichuan.py import for ``data_type=torch.int8``.  The fp16/fp32 ops of the reference module
+(GatedFeedForwardNetwork, Embedding, the BERT/GPT-2/T5 ops) are not part of this path.
+
+Additions that the reference does not have, all optional: `tp` (a tensor-parallel handle, see
+eet_b200.tp) on MetaDesc, and device-resident step counters so that a decode step can be replayed as a
+CUDA graph (eet_b200.modeling).
+"""
+import math
+
+import torch
+
+from . import _lib
+from ._lib import EETError, check, lib
+
+__all__ = ["MetaDesc", "LlamaMmha", "BaichuanMmha", "GatedFeedForwardNetworkInt8", "LayerNorm", "quant_weights",
+           "preprocess_weights", "unpack_weights", "repack_reference_weights", "gemm_w8a16", "EETError"]
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(t):
+    """Device address of a tensor, or None (NULL) for an empty one - the reference turns
+    torch.empty(0) arguments into nullptr the same way (csrc/op/llama_mmha.cpp:27-36,46)."""
+    if t is None or t.numel() == 0:
+        return None
+    return t.data_ptr()
+
+
+# ---------------------------------------------------------------------------------------------------
+# buffer pool (the reference's MManager, csrc/op/mmanager.hpp:118-224): named scratch buffers shared by
+# all ops of a device; a request larger than the cached buffer replaces it.
+# ---------------------------------------------------------------------------------------------------
+class _Pool:
+    def __init__(self):
+        self.buffers = {}
+        self.gemm_ws = {}
+        self.step_arena = {}
+
+    def get(self, name, numel, dtype, device):
+        key = (name, str(device), dtype)
+        buf = self.buffers.get(key)
+        if buf is None or buf.numel() < numel:
+            buf = torch.empty(max(int(numel), 1), dtype=dtype, device=device)
+            self.buffers[key] = buf
+        return buf
+
+    def gemm_workspace(self, nbytes, device):
+        """Zero-initialised split-K scratch; the GEMM leaves it zero after every call."""
+        key = str(device)
+        buf = self.gemm_ws.get(key)
+        if buf is None or buf.numel() < nbytes:
+            buf = torch.zeros(int(nbytes), dtype=torch.uint8, device=device)
+            self.gemm_ws[key] = buf
+        return buf
+
+    def new_step_slot(self, device):
+        """One int32 of a per-device arena; the arena is contiguous so that one launch advances all slots."""
+        key = str(device)
+        arena = self.step_arena.get(key)
+        if arena is None:
+            arena = {"tensor": torch.zeros(4096, dtype=torch.int32, device=device), "used": 0}
+            self.step_arena[key] = arena
+        if arena["used"] >= arena["tensor"].numel():
+            raise EETError("step arena exhausted: more than 4096 attention ops on one device")
+        idx = arena["used"]
+        arena["used"] += 1
+        return arena["tensor"], idx
+
+    def clear(self):
+        self.buffers.clear()
+        self.gemm_ws.clear()
+
+
+_pool = _Pool()
+
+
+def clear_buffers():
+    """Drops the pooled scratch buffers (MManager::clear, csrc/op/mmanager.hpp:211-214)."""
+    _pool.clear()
+
+
+# ---------------------------------------------------------------------------------------------------
+# quantizer / packer entry points
+# ---------------------------------------------------------------------------------------------------
+def _check_quant_input(weight, quant_type):
+    # the checks of symmetric_quantize_last_axis_of_tensor (fpA_intB_gemm_wrapper.cu:31-44)
+    if not weight.is_contiguous():
+        raise RuntimeError("weight must be contiguous")
+    if weight.numel() == 0:
+        raise RuntimeError("weight should not be empty tensor")
+    if weight.dim() not in (2, 3):
+        raise RuntimeError("Invalid dim. The dim of weight should be 2 or 3")
+    if weight.dtype not in (torch.float16, torch.float32):
+        raise RuntimeError("Invalid datatype. Weight must be FP16 or FP32")
+    if quant_type != torch.int8:
+        raise RuntimeError("Must be int8 quantization (the int4 path of the reference is not part of this library)")
+
+
+def quant_weights(origin_weight, quant_type=torch.int8, return_unprocessed_quantized_tensor=False, variant=0,
+                  device=None):
+    """EET.quant_weights (csrc/py11/eet2py.cpp:152-155 -> symmetric_quantize_last_axis_of_tensor,
+    3rdparty/cutlass_kernels/fpA_intB_gemm_wrapper.cu:27-105).
+
+    origin_weight: contiguous fp16/fp32 [K, N] (or [E, K, N]), on the CPU as the reference requires; a
+    CUDA tensor is accepted too.  Returns [packed int8 [K,N], scales [N]] or, with
+    return_unprocessed_quantized_tensor, [row-major int8, packed, scales]; results live where the input
+    lives.  `packed` holds the W8T64 bytes this library's GEMM consumes (opaque, like the reference's).
+    The int8 values and scales are bit-identical to the reference's.  variant=1 selects amax/127 with
+    clip [-127,127] instead of the reference's amax/128, [-128,127]."""
+    _check_quant_input(origin_weight, quant_type)
+    src_device = origin_weight.device
+    dev = torch.device(device) if device is not None else (
+        src_device if src_device.type == "cuda" else torch.device("cuda", torch.cuda.current_device()))
+    w = origin_weight.to(dev)
+    three_d = w.dim() == 3
+    w3 = w if three_d else w.unsqueeze(0)
+    E, K, N = w3.shape
+    if K % 64 or N % 64:
+        raise RuntimeError(f"quant_weights: K={K} and N={N} must be multiples of 64")
+    q = torch.empty((E, K, N), dtype=torch.int8, device=dev) if return_unprocessed_quantized_tensor else None
+    packed = torch.empty((E, K, N), dtype=torch.int8, device=dev)
+    scales = torch.empty((E, N), dtype=w.dtype, device=dev)
+    ws_bytes = lib.eet_quantize_w8_workspace_bytes(K, N)
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
+    with torch.cuda.device(dev):
+        for e in range(E):
+            check(lib.eet_quantize_w8(w3[e].data_ptr(), int(w.dtype == torch.float32), K, N,
+                                      q[e].data_ptr() if q is not None else None, packed[e].data_ptr(),
+                                      scales[e].data_ptr(), variant, ws.data_ptr(), ws_bytes, _stream()))
+    outs = ([q] if q is not None else []) + [packed, scales]
+    outs = [o if three_d else o[0] for o in outs]
+    if src_device.type != "cuda":
+        outs = [o.cpu() for o in outs]
+    return outs
+
+
+def preprocess_weights(origin_weight, is_int4=False):
+    """EET.preprocess_weights (csrc/py11/eet2py.cpp:148-150 -> preprocess_weights_cuda,
+    fpA_intB_gemm_wrapper.cu:107-126): row-major int8 [K, N] -> packed bytes of the same shape."""
+    if is_int4:
+        raise RuntimeError("int4 packing is not part of this library")
+    if origin_weight.dtype != torch.int8 or origin_weight.dim() != 2:
+        raise RuntimeError("preprocess_weights expects a 2-D int8 tensor")
+    src_device = origin_weight.device
+    w = origin_weight.contiguous()
+    w = w if w.is_cuda else w.cuda()
+    K, N = w.shape
+    out = torch.empty_like(w)
+    with torch.cuda.device(w.device):
+        check(lib.eet_pack_w8(w.data_ptr(), K, N, out.data_ptr(), _stream()))
+    return out if src_device.type == "cuda" else out.cpu()
+
+
+def unpack_weights(packed):
+    """Inverse of preprocess_weights: W8T64 bytes [K, N] -> row-major int8 [K, N]."""
+    src_device = packed.device
+    p = packed.contiguous()
+    p = p if p.is_cuda else p.cuda()
+    K, N = p.shape
+    out = torch.empty_like(p)
+    with torch.cuda.device(p.device):
+        check(lib.eet_unpack_w8(p.data_ptr(), K, N, out.data_ptr(), _stream()))
+    return out if src_device.type == "cuda" else out.cpu()
+
+
+def repack_reference_weights(ref_packed):
+    """Bytes packed by the reference for sm75-89 (what an `eet_*_int8.pt` file produced by the reference
+    holds) -> W8T64 bytes."""
+    src_device = ref_packed.device
+    p = ref_packed.contiguous()
+    p = p if p.is_cuda else p.cuda()
+    K, N = p.shape
+    out = torch.empty_like(p)
+    with torch.cuda.device(p.device):
+        check(lib.eet_repack_ref_w8(p.data_ptr(), K, N, out.data_ptr(), _stream()))
+    return out if src_device.type == "cuda" else out.cpu()
+
+
+# ---------------------------------------------------------------------------------------------------
+# GEMM helper shared by the ops
+# ---------------------------------------------------------------------------------------------------
+def gemm_w8a16(x, packed_w, scale, out=None, residual=None):
+    """out[M, N] = x[M, K] @ dequant(packed_w) (+ residual).  x fp16 CUDA contiguous; packed_w int8 [K, N]
+    W8T64 bytes; scale fp16 [N].  The functional form of fastertransformer::gemm_fp16_int_bias_act as the
+    ops call it (csrc/op/llama_mmha.cpp:319-331)."""
+    K, N = packed_w.shape
+    M = x.numel() // K
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.float16, device=x.device)
+    ws_bytes = lib.eet_gemm_w8a16_workspace_bytes(M, N, K)
+    ws = _pool.gemm_workspace(ws_bytes, x.device)
+    check(lib.eet_gemm_w8a16(x.data_ptr(), packed_w.data_ptr(), scale.data_ptr(), out.data_ptr(), M, N, K,
+                             _ptr(residual), 1 if residual is not None else 0, ws.data_ptr(), ws.numel(), _stream()))
+    return out
+
+
+# ---------------------------------------------------------------------------------------------------
+# MetaDesc
+# ---------------------------------------------------------------------------------------------------
+class MetaDesc:
+    """Shape / dtype descriptor handed to every op (csrc/op/meta_desc.hpp:9-101, binding
+    csrc/py11/eet2py.cpp:26-42).  max_seq_len is the prompt cap (sizes scratch), max_full_seq_len the
+    KV-cache length.  Only dtype=torch.float16 with is_int8=True is served by this library.
+
+    `tp` (not in the reference) is an optional eet_b200.tp.TensorParallel handle: the ops then treat their
+    weights as this rank's shard (head_num / d_ff already divided by the caller) and all-reduce the output
+    of the row-parallel projections before the residual is added."""
+
+    def __init__(self, dtype, batch_size, head_num, hidden_units, layer_num, max_seq_len, max_full_seq_len=1,
+                 activation_fn="gelu", d_kv=0, d_ff=0, cuda_device="cuda:0", requires_grad=False, layernorm_eps=1e-6,
+                 is_int8=False, tp=None):
+        if not (batch_size > 0 and head_num > 0 and layer_num > 0 and max_seq_len > 0 and max_full_seq_len > 0):
+            raise RuntimeError("MetaDesc: batch_size, head_num, layer_num, max_seq_len, max_full_seq_len must be > 0")
+        if requires_grad:
+            raise RuntimeError("EET now only support inference")
+        self.dtype = dtype
+        self.batch_size = int(batch_size)
+        self.head_num = int(head_num)
+        self.hidden_units = int(hidden_units)
+        self.layer_num = int(layer_num)
+        self.max_seq_len = int(max_seq_len)
+        self.max_full_seq_len = int(max_full_seq_len)
+        self.activation_fn = activation_fn
+        self.d_kv = int(d_kv)
+        self.d_ff = int(d_ff)
+        self.device = torch.device(cuda_device)
+        if self.device.type != "cuda":
+            raise RuntimeError("EET now only support CUDA")
+        self.layernorm_eps = float(layernorm_eps)
+        self.is_int8 = bool(is_int8)
+        self.tp = tp
+
+    def _require_int8_half(self, who):
+        if self.dtype != torch.float16 or not self.is_int8:
+            raise RuntimeError(f"{who}: this library serves dtype=torch.float16 with is_int8=True only")
+
+
+def _rmsnorm(x2d, gamma, eps, out):
+    M, n = x2d.shape
+    check(lib.eet_rmsnorm(x2d.data_ptr(), gamma.data_ptr(), out.data_ptr(), M, n, eps, _stream()))
+    return out
+
+
+# ---------------------------------------------------------------------------------------------------
+# attention ops
+# ---------------------------------------------------------------------------------------------------
+class _MmhaBase:
+    """State and flow shared by LlamaMmha and BaichuanMmha: RMSNorm -> W8A16 QKV GEMM -> (rotary) ->
+    attention over the per-layer KV cache -> W8A16 output GEMM + residual
+    (csrc/op/llama_mmha.cpp:114-266, csrc/op/baichuan_mmha.cpp:80-216)."""
+
+    ROPE = True
+
+    def __init__(self, desc, QKV_weights, QKV_scale, Q_bias, K_bias, V_bias, Output_weights, Output_scale,
+                 Output_bias, layernorm_weights, layernorm_bias):
+        desc._require_int8_half(type(self).__name__)
+        for name, b in (("Q_bias", Q_bias), ("K_bias", K_bias), ("V_bias", V_bias), ("Output_bias", Output_bias),
+                        ("layernorm_bias", layernorm_bias)):
+            if b is not None and b.numel() != 0:
+                # the half-precision rotary kernel of the reference refuses biases as well
+                # (csrc/core/self_add_bias.cu:479-481); LLaMA/Baichuan have none
+                raise RuntimeError(f"{type(self).__name__}: {name} must be empty (RMSNorm, bias-free projections)")
+        self.desc = desc
+        # the op keeps the tensors alive itself; the reference keeps raw pointers and relies on Python
+        self.qkv_w, self.qkv_s = QKV_weights, QKV_scale
+        self.out_w, self.out_s = Output_weights, Output_scale
+        self.ln_w = layernorm_weights
+        if desc.d_kv == 0:
+            self.size_per_head = desc.hidden_units // desc.head_num
+            self.inner_dim = desc.hidden_units
+        else:
+            self.size_per_head = desc.d_kv
+            self.inner_dim = desc.d_kv * desc.head_num
+        if self.size_per_head != 128:
+            raise RuntimeError("attention: only head size 128 is supported")
+        for t, shape, what in ((self.qkv_w, (desc.hidden_units, 3 * self.inner_dim), "QKV_weights"),
+                               (self.out_w, (self.inner_dim, desc.hidden_units), "Output_weights")):
+            if tuple(t.shape) != shape or t.dtype != torch.int8 or not t.is_cuda:
+                raise RuntimeError(f"{what} must be a CUDA int8 tensor of shape {shape}, got {tuple(t.shape)} {t.dtype}")
+        dev = desc.device
+        H, D, T = desc.head_num, self.size_per_head, desc.max_full_seq_len
+        # per-layer caches, [batch][head][time][dim] so that one (batch, head) history is contiguous
+        self.k_cache = torch.zeros((desc.batch_size, H, T, D), dtype=torch.float16, device=dev)
+        self.v_cache = torch.zeros_like(self.k_cache)
+        self.step_ = 1
+        self._arena, self._slot = _pool.new_step_slot(dev)
+        self.use_device_step = False
+        self.rope_base = 10000.0
+        self._slopes = None
+
+    # -- helpers ------------------------------------------------------------------------------------
+    def _project(self, ctx2d, inp, B, S):
+        """Output projection + residual (LlamaMmha::project, llama_mmha.cpp:428-469: the residual is added
+        whatever add_residual says)."""
+        d = self.desc
+        out = _pool.get("self_mask_attn_cache", d.batch_size * d.max_seq_len * d.hidden_units, torch.float16, d.device)
+        out = out[: B * S * d.hidden_units].view(B * S, d.hidden_units)
+        inp2d = inp.reshape(B * S, d.hidden_units)
+        if d.tp is None or d.tp.size == 1:
+            gemm_w8a16(ctx2d, self.out_w, self.out_s, out=out, residual=inp2d)
+        else:
+            gemm_w8a16(ctx2d, self.out_w, self.out_s, out=out)
+            d.tp.all_reduce(out)
+            check(lib.eet_add_residual(out.data_ptr(), inp2d.data_ptr(), out.numel(), _stream()))
+        return out.view(B, S, d.hidden_units)
+
+    def _check_input(self, inp):
+        d = self.desc
+        if inp.dtype != torch.float16 or not inp.is_cuda or inp.dim() != 3 or inp.shape[2] != d.hidden_units:
+            raise RuntimeError("input must be a CUDA fp16 tensor [batch, seq, hidden]")
+        if not inp.is_contiguous():
+            raise RuntimeError("input must be contiguous")
+        if inp.shape[0] > d.batch_size:
+            raise RuntimeError("cur_batch_size_ must be less than or equal to max_batch_size_")
+
+    def forward(self, input, pre_padding_len, reorder_state, pre_layernorm, add_residual, first_pass,
+                relative_attention_bias=None):
+        """Same signature as the reference (csrc/py11/eet2py.cpp:73-86).  pre_layernorm / add_residual are
+        accepted and ignored exactly as the reference ignores them: the norm always comes first and the
+        residual is always added."""
+        self._check_input(input)
+        with torch.cuda.device(self.desc.device):
+            if first_pass:
+                return self._forward_full(input, pre_padding_len, relative_attention_bias)
+            return self._forward_inc(input, pre_padding_len, reorder_state, relative_attention_bias)
+
+    __call__ = forward
+
+    def _forward_full(self, inp, pre_padding_len, bias):
+        d = self.desc
+        B, S, h = inp.shape
+        if S > d.max_seq_len or S > d.max_full_seq_len:
+            raise RuntimeError("cur_seq_len must be less than or equal to max_seq_len / max_full_seq_len")
+        H, D = d.head_num, self.size_per_head
+        M = B * S
+        cap = d.batch_size * d.max_seq_len
+        xn = _pool.get("layernorm", cap * h, torch.float16, d.device)[: M * h].view(M, h)
+        _rmsnorm(inp.view(M, h), self.ln_w, d.layernorm_eps, xn)
+        qkv = _pool.get("qkv_full", cap * 3 * self.inner_dim, torch.float16, d.device)[: M * 3 * self.inner_dim]
+        qkv = qkv.view(M, 3 * self.inner_dim)
+        gemm_w8a16(xn, self.qkv_w, self.qkv_s, out=qkv)
+        q = _pool.get("q_buf", cap * self.inner_dim, torch.float16, d.device)[: M * self.inner_dim]
+        check(lib.eet_qkv_split_store(qkv.data_ptr(), q.data_ptr(), self.k_cache.data_ptr(), self.v_cache.data_ptr(),
+                                      B, S, H, D, d.max_full_seq_len, int(self.ROPE), self.rope_base, _stream()))
+        ctx = _pool.get("dst", cap * self.inner_dim, torch.float16, d.device)[: M * self.inner_dim]
+        alibi = None
+        if not self.ROPE:
+            if bias is None or bias.numel() == 0:
+                raise RuntimeError("BaichuanMmha: relative_attention_bias [H, S, S] is required")
+            if tuple(bias.shape) != (H, S, S) or bias.dtype != torch.float16 or not bias.is_contiguous():
+                raise RuntimeError(f"relative_attention_bias must be contiguous fp16 [{H}, {S}, {S}]")
+            alibi = bias
+        check(lib.eet_prefill_mha(q.data_ptr(), self.k_cache.data_ptr(), self.v_cache.data_ptr(), ctx.data_ptr(),
+                                  B, S, H, D, d.max_full_seq_len, _ptr(pre_padding_len), _ptr(alibi), S, _stream()))
+        out = self._project(ctx.view(M, self.inner_dim), inp, B, S)
+        self.step_ = S
+        return out
+
+    def _forward_inc(self, inp, pre_padding_len, reorder_state, bias):
+        d = self.desc
+        B, S, h = inp.shape
+        if S != 1:
+            raise RuntimeError("incremental decoding takes one token per sequence")
+        self.step_ += 1
+        if self.step_ > d.max_full_seq_len:
+            raise RuntimeError("Exceed the maximum step length")
+        H, D = d.head_num, self.size_per_head
+        xn = _pool.get("layernorm_inc", d.batch_size * h, torch.float16, d.device)[: B * h].view(B, h)
+        _rmsnorm(inp.view(B, h), self.ln_w, d.layernorm_eps, xn)
+        qkv = _pool.get("qkv_inc", d.batch_size * 3 * self.inner_dim, torch.float16, d.device)
+        qkv = qkv[: B * 3 * self.inner_dim].view(B, 3 * self.inner_dim)
+        gemm_w8a16(xn, self.qkv_w, self.qkv_s, out=qkv)
+        if reorder_state is not None and reorder_state.numel() != 0:
+            self._reorder(reorder_state, B)
+        ctx = _pool.get("context_buf", d.batch_size * self.inner_dim, torch.float16, d.device)[: B * self.inner_dim]
+        alibi, alibi_stride, slopes = None, 0, None
+        if not self.ROPE:
+            if self.use_device_step:
+                slopes = self._alibi_slopes()
+            else:
+                if bias is None or bias.numel() == 0:
+                    raise RuntimeError("BaichuanMmha: relative_attention_bias [H, 1, step] is required")
+                if bias.shape[0] != H or bias.shape[-1] < self.step_ or not bias.is_contiguous():
+                    raise RuntimeError(f"relative_attention_bias must be contiguous fp16 [{H}, 1, >={self.step_}]")
+                alibi, alibi_stride = bias, bias.shape[-1]
+        step_dev = None
+        if self.use_device_step:
+            step_dev = self._arena.data_ptr() + 4 * self._slot
+        check(lib.eet_decode_mha(qkv.data_ptr(), self.k_cache.data_ptr(), self.v_cache.data_ptr(), ctx.data_ptr(),
+                                 B, H, D, d.max_full_seq_len, self.step_, step_dev, _ptr(pre_padding_len),
+                                 _ptr(alibi), alibi_stride, _ptr(slopes), int(self.ROPE), self.rope_base, 0,
+                                 _stream()))
+        return self._project(ctx.view(B, self.inner_dim), inp, B, 1)
+
+    def _reorder(self, reorder_state, B):
+        """Beam search: reorder the cache rows first, as LlamaMmha::forward_inc does
+        (llama_mmha.cpp:250-252); step_ already counts the token being added, whose slot is still empty."""
+        d = self.desc
+        H, D = d.head_num, self.size_per_head
+        hist = self.step_ - 1
+        nbytes = lib.eet_reorder_kv_workspace_bytes(B, H, D, hist)
+        ws = _pool.get("reorder_ws", nbytes // 2, torch.float16, d.device)
+        idx = reorder_state.to(device=d.device, dtype=torch.int64).contiguous()
+        check(lib.eet_reorder_kv(self.k_cache.data_ptr(), self.v_cache.data_ptr(), idx.data_ptr(), B, H, D,
+                                 d.max_full_seq_len, hist, ws.data_ptr(), nbytes, _stream()))
+
+    def _alibi_slopes(self):
+        return self._slopes
+
+    # -- device-resident step (used by the CUDA-graph decode path) -------------------------------------
+    def sync_device_step(self):
+        """Copies the host step counter into this op's device slot."""
+        self._arena[self._slot] = self.step_
+
+
+class LlamaMmha(_MmhaBase):
+    """EET.LlamaMmha (csrc/py11/eet2py.cpp:73-86, csrc/op/llama_mmha.{hpp,cpp}): LLaMA / Baichuan-7B
+    attention block with NeoX rotary embedding."""
+    ROPE = True
+
+
+class BaichuanMmha(_MmhaBase):
+    """EET.BaichuanMmha (csrc/py11/eet2py.cpp:58-71, csrc/op/baichuan_mmha.{hpp,cpp}): Baichuan-13B
+    attention block, no rotary embedding, ALiBi bias passed as relative_attention_bias."""
+    ROPE = False
+
+    def set_alibi_slopes(self, slopes):
+        """fp32 [head_num] slopes of this op's heads; lets the decode kernel form the bias row
+        fp16(slope * t) itself, which is what the mask the reference's Python builds contains
+        (python/eet/transformers/modeling_baichuan.py:70-80)."""
+        self._slopes = slopes.to(device=self.desc.device, dtype=torch.float32).contiguous()
+
+
+# ---------------------------------------------------------------------------------------------------
+# feed-forward op
+# ---------------------------------------------------------------------------------------------------
+class GatedFeedForwardNetworkInt8:
+    """EET.GatedFeedForwardNetworkInt8 (csrc/py11/eet2py.cpp:126-134, csrc/op/gated_ffn_int8.{hpp,cpp}):
+    RMSNorm -> act(x.W0) * (x.W1) -> .W_out (+ residual)."""
+
+    def __init__(self, desc, Intermediate_0_weights, Intermediate_0_scale, Intermediate_0_bias,
+                 Intermediate_1_weights, Intermediate_1_scale, Intermediate_1_bias, Output_weights, Output_scale,
+                 Output_bias, layernorm_weights, layernorm_bias, ffn_cache_name="out_cache"):
+        desc._require_int8_half("GatedFeedForwardNetworkInt8")
+        if desc.activation_fn != "silu":
+            # the reference prints "unsupported activation" for unknown names and supports gelu/relu gates
+            # too (gated_ffn_int8.cpp:40-61); the LLaMA/Baichuan path uses silu only
+            raise RuntimeError(f"GatedFeedForwardNetworkInt8: activation '{desc.activation_fn}' is not supported (silu only)")
+        for name, b in (("Intermediate_0_bias", Intermediate_0_bias), ("Intermediate_1_bias", Intermediate_1_bias),
+                        ("Output_bias", Output_bias), ("layernorm_bias", layernorm_bias)):
+            if b is not None and b.numel() != 0:
+                raise RuntimeError(f"GatedFeedForwardNetworkInt8: {name} must be empty")
+        self.desc = desc
+        self.d_ff = desc.d_ff if desc.d_ff != 0 else desc.hidden_units * 4
+        self.w0, self.s0 = Intermediate_0_weights, Intermediate_0_scale
+        self.w1, self.s1 = Intermediate_1_weights, Intermediate_1_scale
+        self.w_out, self.s_out = Output_weights, Output_scale
+        self.ln_w = layernorm_weights
+        self.cache_name = ffn_cache_name
+        h = desc.hidden_units
+        for t, shape, what in ((self.w0, (h, self.d_ff), "Intermediate_0_weights"),
+                               (self.w1, (h, self.d_ff), "Intermediate_1_weights"),
+                               (self.w_out, (self.d_ff, h), "Output_weights")):
+            if tuple(t.shape) != shape or t.dtype != torch.int8 or not t.is_cuda:
+                raise RuntimeError(f"{what} must be a CUDA int8 tensor of shape {shape}, got {tuple(t.shape)} {t.dtype}")
+
+    def forward(self, input, pre_layernorm=True, add_residual=True):
+        d = self.desc
+        if input.dtype != torch.float16 or not input.is_cuda or not input.is_contiguous():
+            raise RuntimeError("input must be a contiguous CUDA fp16 tensor [batch, seq, hidden]")
+        if not pre_layernorm:
+            raise RuntimeError("GatedFeedForwardNetworkInt8: the post-layernorm form is not part of the int8 LLaMA path")
+        B, S, h = input.shape
+        M = B * S
+        cap = d.batch_size * d.max_seq_len
+        with torch.cuda.device(d.device):
+            xn = _pool.get("layernorm_tensor", cap * h, torch.float16, d.device)[: M * h].view(M, h)
+            _rmsnorm(input.view(M, h), self.ln_w, d.layernorm_eps, xn)
+            act = _pool.get("ffn_inner_act", cap * self.d_ff, torch.float16, d.device)[: M * self.d_ff].view(M, self.d_ff)
+            lin = _pool.get("ffn_inner_linear", cap * self.d_ff, torch.float16, d.device)[: M * self.d_ff].view(M, self.d_ff)
+            gemm_w8a16(xn, self.w0, self.s0, out=act)
+            gemm_w8a16(xn, self.w1, self.s1, out=lin)
+            check(lib.eet_swiglu(act.data_ptr(), lin.data_ptr(), M, self.d_ff, _stream()))
+            out = _pool.get(self.cache_name, cap * h, torch.float16, d.device)[: M * h].view(M, h)
+            inp2d = input.view(M, h)
+            if d.tp is None or d.tp.size == 1:
+                gemm_w8a16(act, self.w_out, self.s_out, out=out, residual=inp2d if add_residual else None)
+            else:
+                gemm_w8a16(act, self.w_out, self.s_out, out=out)
+                d.tp.all_reduce(out)
+                if add_residual:
+                    check(lib.eet_add_residual(out.data_ptr(), inp2d.data_ptr(), out.numel(), _stream()))
+        return out.view(B, S, h)
+
+    __call__ = forward
+
+
+# ---------------------------------------------------------------------------------------------------
+# LayerNorm op
+# ---------------------------------------------------------------------------------------------------
+class LayerNorm:
+    """EET.LayerNorm (csrc/py11/eet2py.cpp:143-145, csrc/op/layer_norm.cpp:8-33).  With an empty beta it is
+    RMSNorm, the only form on the LLaMA/Baichuan path; the op owns its output tensor
+    [batch, max_seq_len, hidden]."""
+
+    def __init__(self, desc, gamma, beta):
+        if desc.dtype != torch.float16:
+            raise RuntimeError("LayerNorm: fp16 only")
+        if beta is not None and beta.numel() != 0:
+            raise RuntimeError("LayerNorm: only the RMSNorm form (empty beta) is part of this library")
+        self.desc = desc
+        self.gamma = gamma
+        self.output = torch.zeros((desc.batch_size, desc.max_seq_len, desc.hidden_units), dtype=torch.float16,
+                                  device=desc.device)
+
+    def layer_norm(self, input_tensor):
+        B, S, h = input_tensor.shape
+        out = self.output.view(-1)[: B * S * h].view(B * S, h)
+        with torch.cuda.device(self.desc.device):
+            _rmsnorm(input_tensor.reshape(B * S, h), self.gamma, self.desc.layernorm_eps, out)
+        return out.view(B, S, h)
+
+
+def alibi_slopes(n_head):
+    """Slopes of _get_interleave (python/eet/transformers/modeling_baichuan.py:51-64)."""
+    def pow2(n):
+        start = 2 ** (-(2 ** -(math.log2(n) - 3)))
+        return [start * start ** i for i in range(n)]
+    if math.log2(n_head).is_integer():
+        return pow2(n_head)
+    c = 2 ** math.floor(math.log2(n_head))
+    return pow2(c) + alibi_slopes(2 * c)[0::2][: n_head - c]

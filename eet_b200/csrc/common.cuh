@@ -1,0 +1,174 @@
+// Shared device/host helpers for the sm_100a kernels of this library: error plumbing for the C ABI,
+// mbarrier / bulk-copy (TMA engine) wrappers with bounded waits, and the int8 -> fp16 register
+// conversion used by both GEMM kernels.
+#pragma once
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <cstdarg>
+#include <cstdio>
+
+namespace eet {
+
+// ------------------------------------------------------------------------------------------ host errors
+// Every extern "C" entry point returns 0 on success; on failure it returns non-zero and leaves a message
+// that eet_last_error() hands out (thread-local, overwritten by the next failure on the same thread).
+void set_error(const char* fmt, ...);
+
+#define EET_CHECK(cond, ...)                                                                                 \
+    do {                                                                                                     \
+        if (!(cond)) {                                                                                       \
+            ::eet::set_error(__VA_ARGS__);                                                                   \
+            return 1;                                                                                        \
+        }                                                                                                    \
+    } while (0)
+
+#define EET_CUDA(call)                                                                                       \
+    do {                                                                                                     \
+        cudaError_t err__ = (call);                                                                          \
+        if (err__ != cudaSuccess) {                                                                          \
+            ::eet::set_error("%s failed: %s (%s:%d)", #call, cudaGetErrorString(err__), __FILE__, __LINE__); \
+            return 2;                                                                                        \
+        }                                                                                                    \
+    } while (0)
+
+#define EET_LAUNCH_CHECK() EET_CUDA(cudaGetLastError())
+
+// Device-side status word.  A kernel whose bounded wait ran out stores a non-zero code here and returns;
+// the host reads it with eet_device_status().  Codes: 1 = GEMM pipeline wait, 2 = tensor-core GEMM wait.
+// (The library is built as one translation unit, so this definition is seen exactly once.)
+#ifdef __CUDACC__
+__device__ int g_device_status = 0;
+#endif
+
+int sm_count();  // multiprocessors of the current device (cached per device)
+
+// ------------------------------------------------------------------------------------------ device helpers
+#ifdef __CUDACC__
+
+constexpr int kTile = 64;              // W8T64 tile edge (channels and reduction indices)
+constexpr int kTileBytes = kTile * kTile;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p)
+{
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+
+__device__ __forceinline__ void mbar_fence_init()
+{
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+                 : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
+// Waits for the phase with the given parity to complete, but never forever: after kSpinLimit failed
+// polls it gives up and returns false.  Each failed try_wait already blocks for a hardware-defined
+// interval, so the limit amounts to a second or more of wall time.
+constexpr uint32_t kSpinLimit = 1u << 22;
+
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity)
+{
+    for (uint32_t i = 0; i < kSpinLimit; ++i) {
+        if (mbar_try_wait(bar, parity)) {
+            return true;
+        }
+    }
+    return false;
+}
+
+// 1-D bulk copy global -> shared through the TMA engine; completion is signalled on `bar` as
+// transaction bytes.  Both addresses must be 16-byte aligned and `bytes` a multiple of 16.
+__device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gmem_src, uint32_t bytes, uint64_t* bar)
+{
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                     smem_u32(smem_dst)),
+                 "l"(gmem_src), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
+
+// Same with an L2 evict-first hint for data that is streamed once (the weights).
+__device__ __forceinline__ void bulk_g2s_stream(void* smem_dst, const void* gmem_src, uint32_t bytes, uint64_t* bar)
+{
+    uint64_t policy;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;" ::"r"(
+            smem_u32(smem_dst)),
+        "l"(gmem_src), "r"(bytes), "r"(smem_u32(bar)), "l"(policy)
+        : "memory");
+}
+
+// Four biased bytes (value + 128 each) -> four fp16 values, as two half2 registers {b0,b1} and {b2,b3}.
+// Placing a byte under the exponent pattern 0x64 yields the fp16 number 1024 + byte; subtracting 1152
+// gives byte - 128 exactly.
+__device__ __forceinline__ void cvt_u8x4_to_f16x4(uint32_t w, uint32_t& lo, uint32_t& hi)
+{
+    const uint32_t magic = 0x64646464u;
+    const uint32_t bias = 0x64806480u;  // {1152, 1152} in fp16
+    uint32_t a, b;
+    asm("prmt.b32 %0, %1, %2, 0x4140;" : "=r"(a) : "r"(w), "r"(magic));
+    asm("prmt.b32 %0, %1, %2, 0x4342;" : "=r"(b) : "r"(w), "r"(magic));
+    asm("sub.f16x2 %0, %1, %2;" : "=r"(lo) : "r"(a), "r"(bias));
+    asm("sub.f16x2 %0, %1, %2;" : "=r"(hi) : "r"(b), "r"(bias));
+}
+
+__device__ __forceinline__ void mma_m16n8k16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                             uint32_t b0, uint32_t b1)
+{
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ float warp_sum(float v)
+{
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        v += __shfl_xor_sync(0xffffffffu, v, o);
+    }
+    return v;
+}
+
+__device__ __forceinline__ float warp_max(float v)
+{
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    }
+    return v;
+}
+
+#endif  // __CUDACC__
+
+}  // namespace eet

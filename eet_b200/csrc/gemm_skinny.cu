@@ -1,0 +1,277 @@
+// W8A16 skinny GEMM for the decode regime (M <= 16 per pass): C[M,N] = A[M,K] (fp16) x dequant(B),
+// B in the W8T64 layout, fp16 per-channel scale applied once per output.
+//
+// Replaces the reference's fpA_intB GEMM (3rdparty/cutlass_kernels/fpA_intB_gemm/fpA_intB_gemm_template.h
+// :48-177, kernel cutlass_extensions/.../gemm/kernel/fpA_intB_gemm.h:60-486) for small M, where that
+// kernel pads M to a 32-row tile and launches only N/128 CTAs with no split-K (cutlass_heuristic.cc
+// :80-84), far too few bytes in flight for HBM.
+//
+// B200 design.  The job is HBM-bound: N*K weight bytes are read once.
+//  * Stream-K partition: the W8T64 tiles are numbered [N/64][K/64] in memory order; the grid is one
+//    persistent CTA per SM and CTA c owns an equal, contiguous run of tiles, i.e. one linear byte range
+//    of the weight array, whatever N and K are.
+//  * A producer warp feeds a ring of shared-memory stages with 1-D bulk copies (TMA engine,
+//    cp.async.bulk + mbarrier complete_tx): up to 32 KiB of weights plus the matching slice of the
+//    activations per stage, 4-5 stages in flight per SM.
+//  * Eight consumer warps each take one 64x64 tile of a stage: 16-byte shared loads deliver exactly the
+//    B fragments of mma.m16n8k16 (8 channels x 64 reduction indices per load), bytes become fp16 in
+//    registers (prmt + sub.f16x2) and feed the tensor cores with the activations as the A operand; the
+//    reduction index is permuted identically on both operands, so no shuffles or transposes are needed.
+//  * When a CTA's run ends inside a tile row, partial sums go to an fp32 scratch with red.global.add and
+//    a per-tile-row arrival counter; the CTA that completes the count applies the scale (and residual),
+//    writes fp16, and restores the scratch to zero.  Tile rows covered by one CTA skip the scratch.
+//
+// Numerics: products of fp16 activations with exact integer weights, fp32 accumulation, one multiply by
+// the fp16 scale, one rounding to fp16 (the reference rounds every q*scale to fp16 first and rounds the
+// fp32 accumulator once: mma_tensorop_dequantizer.h:259-274, epilogue_helpers.h:73-80).
+#include "common.cuh"
+#include "kernels.h"
+
+namespace eet {
+
+namespace {
+
+constexpr int kConsumerWarps = 8;
+constexpr int kConsumerThreads = kConsumerWarps * 32;
+constexpr int kSkinnyThreads = kConsumerThreads + 32;
+constexpr int kStageTiles = 8;                       // W8T64 tiles per stage
+constexpr int kStageWBytes = kStageTiles * kTileBytes;
+constexpr int kXRowBytes = kStageTiles * 128 + 16;   // 8 tiles x 64 halves, padded: conflict-free A loads
+constexpr int kMaxStages = 6;
+
+__host__ __device__ constexpr int stage_bytes(int mt)
+{
+    return kStageWBytes + mt * kXRowBytes;
+}
+
+struct SkinnySmem {
+    uint64_t full[kMaxStages];
+    uint64_t empty[kMaxStages];
+    float tile[16][64];  // cross-warp accumulation of one tile row's [rows][64 channels]
+    int flag;
+    volatile int abort;
+};
+
+__device__ __forceinline__ void consumer_bar()
+{
+    asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
+}
+
+template<int MT>
+__global__ void __launch_bounds__(kSkinnyThreads, 1)
+gemm_skinny_kernel(GemmArgs a, int n_stages)
+{
+    extern __shared__ __align__(128) uint8_t dyn_smem[];
+    __shared__ SkinnySmem sm;
+
+    const int KT = a.K / kTile, NT = a.N / kTile;
+    const long long G = (long long)NT * KT;
+    const int g0 = (int)(G * blockIdx.x / gridDim.x);
+    const int g1 = (int)(G * (blockIdx.x + 1) / gridDim.x);
+    const int m0 = blockIdx.y * 16;
+    const int rows = min(MT, a.M - m0);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < n_stages; ++s) {
+            mbar_init(&sm.full[s], 1);
+            mbar_init(&sm.empty[s], kConsumerWarps);
+        }
+        sm.abort = 0;
+        mbar_fence_init();
+    }
+    for (int e = threadIdx.x; e < 16 * 64; e += blockDim.x) (&sm.tile[0][0])[e] = 0.f;
+    __syncthreads();
+
+    if (warp == kConsumerWarps) {
+        // ------------------------------------------------------------------ producer warp
+        int it = 0;
+        for (int g = g0; g < g1; ++it) {
+            const int nt = g / KT, kb = g - nt * KT;
+            const int nb = min(min(kStageTiles, KT - kb), g1 - g);
+            const int s = it % n_stages;
+            if (it >= n_stages && !sm.abort) {
+                if (!mbar_wait_bounded(&sm.empty[s], ((it / n_stages) - 1) & 1)) {
+                    sm.abort = 1;
+                    g_device_status = 1;
+                }
+            }
+            uint8_t* stage = dyn_smem + (size_t)s * stage_bytes(MT);
+            if (lane == 0) {
+                mbar_arrive_expect_tx(&sm.full[s], (uint32_t)(nb * kTileBytes + rows * nb * 128));
+            }
+            __syncwarp();
+            if (lane == 0) {
+                bulk_g2s_stream(stage, a.B + (size_t)g * kTileBytes, (uint32_t)(nb * kTileBytes), &sm.full[s]);
+            }
+            if (lane < rows) {
+                bulk_g2s(stage + kStageWBytes + lane * kXRowBytes, a.A + (size_t)(m0 + lane) * a.K + (size_t)kb * kTile,
+                         (uint32_t)(nb * 128), &sm.full[s]);
+            }
+            g += nb;
+        }
+        return;
+    }
+
+    // ---------------------------------------------------------------------- consumer warps
+    const int gq = lane >> 2, tq = lane & 3;  // mma fragment coordinates
+    float acc[8][4];
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) acc[j][c] = 0.f;
+
+    int it = 0;
+    int tile_first_kb = -1;  // first k-tile of the current tile row handled by this CTA
+    for (int g = g0; g < g1; ++it) {
+        const int nt = g / KT, kb = g - nt * KT;
+        const int nb = min(min(kStageTiles, KT - kb), g1 - g);
+        const int s = it % n_stages;
+        if (tile_first_kb < 0) tile_first_kb = kb;
+        if (!sm.abort) {
+            if (!mbar_wait_bounded(&sm.full[s], (it / n_stages) & 1)) {
+                sm.abort = 1;
+                g_device_status = 1;
+            }
+        }
+        const uint8_t* stage = dyn_smem + (size_t)s * stage_bytes(MT);
+        if (warp < nb) {
+            // activations: rows gq and gq+8, 16 consecutive reduction indices starting at 16*tq
+            const uint8_t* xs = stage + kStageWBytes + warp * 128 + tq * 32;
+            uint4 xa0 = make_uint4(0, 0, 0, 0), xa1 = xa0, xb0 = xa0, xb1 = xa0;
+            if (gq < rows) {
+                xa0 = *reinterpret_cast<const uint4*>(xs + gq * kXRowBytes);
+                xa1 = *reinterpret_cast<const uint4*>(xs + gq * kXRowBytes + 16);
+            }
+            if (MT == 16 && gq + 8 < rows) {
+                xb0 = *reinterpret_cast<const uint4*>(xs + (gq + 8) * kXRowBytes);
+                xb1 = *reinterpret_cast<const uint4*>(xs + (gq + 8) * kXRowBytes + 16);
+            }
+            const uint32_t xa[8] = {xa0.x, xa0.y, xa0.z, xa0.w, xa1.x, xa1.y, xa1.z, xa1.w};
+            const uint32_t xb[8] = {xb0.x, xb0.y, xb0.z, xb0.w, xb1.x, xb1.y, xb1.z, xb1.w};
+            const uint8_t* ws = stage + warp * kTileBytes + lane * 16;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                // 8 channels (8j + gq) x 64 reduction indices: this lane gets indices 16*tq .. 16*tq+15
+                const uint4 wv = *reinterpret_cast<const uint4*>(ws + j * 512);
+                const uint32_t w4[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    uint32_t b0, b1;
+                    cvt_u8x4_to_f16x4(w4[i], b0, b1);
+                    mma_m16n8k16(acc[j], xa[2 * i], xb[2 * i], xa[2 * i + 1], xb[2 * i + 1], b0, b1);
+                }
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sm.empty[s]);
+        g += nb;
+
+        const bool row_end = (kb + nb == KT);
+        if (row_end || g == g1) {
+            // ---- flush the tile row: reduce the 8 warps' fragments through shared memory ----
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int n = j * 8 + tq * 2;
+                atomicAdd(&sm.tile[gq][n], acc[j][0]);
+                atomicAdd(&sm.tile[gq][n + 1], acc[j][1]);
+                if (MT == 16) {
+                    atomicAdd(&sm.tile[gq + 8][n], acc[j][2]);
+                    atomicAdd(&sm.tile[gq + 8][n + 1], acc[j][3]);
+                }
+#pragma unroll
+                for (int c = 0; c < 4; ++c) acc[j][c] = 0.f;
+            }
+            consumer_bar();
+            const bool whole_row = (tile_first_kb == 0) && row_end;
+            const int n_base = nt * kTile;
+            float* ws_tile = a.ws + (size_t)m0 * a.N + n_base;
+            int* counter = reinterpret_cast<int*>(a.ws + (size_t)gridDim.y * 16 * a.N) + blockIdx.y * NT + nt;
+            bool finalize = whole_row;
+            if (!whole_row) {
+                for (int e = threadIdx.x; e < rows * 64; e += kConsumerThreads) {
+                    const int m = e >> 6, n = e & 63;
+                    atomicAdd(ws_tile + (size_t)m * a.N + n, sm.tile[m][n]);
+                }
+                __threadfence();
+                consumer_bar();
+                if (threadIdx.x == 0) {
+                    const int contributed = kb + nb - tile_first_kb;
+                    const int old = atomicAdd(counter, contributed);
+                    sm.flag = (old + contributed == KT);
+                }
+                consumer_bar();
+                finalize = sm.flag != 0;
+                if (finalize) __threadfence();
+            }
+            if (finalize) {
+                for (int e = threadIdx.x; e < rows * 64; e += kConsumerThreads) {
+                    const int m = e >> 6, n = e & 63;
+                    float v;
+                    if (whole_row) {
+                        v = sm.tile[m][n];
+                    }
+                    else {
+                        v = __ldcg(ws_tile + (size_t)m * a.N + n);
+                        __stcg(ws_tile + (size_t)m * a.N + n, 0.f);
+                    }
+                    const size_t o = (size_t)(m0 + m) * a.N + n_base + n;
+                    __half r = __float2half(v * __half2float(a.scale[n_base + n]));
+                    if (a.epilogue == 1) r = __hadd(r, a.residual[o]);
+                    a.C[o] = r;
+                }
+                if (!whole_row && threadIdx.x == 0) *counter = 0;
+            }
+            for (int e = threadIdx.x; e < 16 * 64; e += kConsumerThreads) (&sm.tile[0][0])[e] = 0.f;
+            consumer_bar();
+            tile_first_kb = -1;
+        }
+    }
+}
+
+}  // namespace
+
+size_t skinny_workspace_bytes(int M, int N, int dual)
+{
+    (void)dual;
+    const size_t chunks = (size_t)((M + 15) / 16 > 0 ? (M + 15) / 16 : 1);
+    const size_t chunks_per_launch = chunks < 8 ? chunks : 8;
+    return chunks_per_launch * 16 * (size_t)N * sizeof(float) + chunks_per_launch * (size_t)(N / kTile) * sizeof(int);
+}
+
+int launch_gemm_skinny(const GemmArgs& a, cudaStream_t stream)
+{
+    EET_CHECK(a.epilogue == 0 || a.epilogue == 1, "skinny GEMM: epilogue %d is not supported", a.epilogue);
+    if (a.M == 0) return 0;
+    static bool attr_set[64][2] = {};
+    int dev = 0;
+    EET_CUDA(cudaGetDevice(&dev));
+    dev &= 63;
+    const long long G = (long long)(a.N / kTile) * (a.K / kTile);
+    int grid_x = sm_count();
+    if (grid_x > G) grid_x = (int)G;
+    const int total_chunks = (a.M + 15) / 16;
+    for (int c0 = 0; c0 < total_chunks; c0 += 8) {
+        const int chunks = (total_chunks - c0 < 8) ? (total_chunks - c0) : 8;
+        GemmArgs b = a;
+        b.A = a.A + (size_t)c0 * 16 * a.K;
+        b.C = a.C + (size_t)c0 * 16 * a.N;
+        if (a.residual) b.residual = a.residual + (size_t)c0 * 16 * a.N;
+        b.M = a.M - c0 * 16;
+        if (b.M > chunks * 16) b.M = chunks * 16;
+        const bool mt8 = (b.M <= 8);
+        const int mt = mt8 ? 8 : 16;
+        const int stages = mt8 ? 5 : 4;
+        const size_t smem = (size_t)stages * stage_bytes(mt);
+        auto kern = mt8 ? gemm_skinny_kernel<8> : gemm_skinny_kernel<16>;
+        if (!attr_set[dev][mt8 ? 0 : 1]) {
+            EET_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            attr_set[dev][mt8 ? 0 : 1] = true;
+        }
+        kern<<<dim3(grid_x, chunks), kSkinnyThreads, smem, stream>>>(b, stages);
+        EET_LAUNCH_CHECK();
+    }
+    return 0;
+}
+
+}  // namespace eet

@@ -1,0 +1,266 @@
+// The small kernels between the GEMMs of one decoder layer: RMSNorm, gated SiLU, residual add, the
+// prefill-side QKV split + rotary embedding + KV-cache store, KV-cache reordering for beam search and
+// the device-resident step counters used when a decode step is replayed as a CUDA graph.
+//
+// Each mirrors the arithmetic of a reference kernel (cited per function) and is sized for HBM:
+// 16-byte accesses, one pass over the data where the reference makes two.
+#include "common.cuh"
+#include "kernels.h"
+
+namespace eet {
+
+namespace {
+
+// y = x * rsqrt(mean(x^2) + eps) * gamma, fp32 math, one fp16 rounding.
+// Reference: T5norm1_kernel_opt<half> (csrc/core/layer_norm.cu:490-531).  One CTA per row; the row is
+// kept in registers between the two phases (n <= 8 * 2 * blockDim).
+__global__ void __launch_bounds__(1024)
+rmsnorm_kernel(const __half* __restrict__ x, const __half* __restrict__ gamma, __half* __restrict__ y, int n, float eps)
+{
+    __shared__ float red[32];
+    __shared__ float s_inv;
+    const int row = blockIdx.x;
+    const int nv = n >> 3;
+    const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)row * n);
+    const uint4* g4 = reinterpret_cast<const uint4*>(gamma);
+    uint4* yr = reinterpret_cast<uint4*>(y + (size_t)row * n);
+    uint4 v[2];
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+        const int i = threadIdx.x + j * blockDim.x;
+        if (i < nv) {
+            v[j] = xr[i];
+            const __half2* h = reinterpret_cast<const __half2*>(&v[j]);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float2 f = __half22float2(h[e]);
+                ss += f.x * f.x + f.y * f.y;
+            }
+        }
+    }
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        float t = (threadIdx.x < (blockDim.x >> 5)) ? red[threadIdx.x] : 0.f;
+        t = warp_sum(t);
+        if (threadIdx.x == 0) s_inv = rsqrtf(t / n + eps);
+    }
+    __syncthreads();
+    const float inv = s_inv;
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+        const int i = threadIdx.x + j * blockDim.x;
+        if (i < nv) {
+            const uint4 g = g4[i];
+            const __half2* h = reinterpret_cast<const __half2*>(&v[j]);
+            const __half2* gh = reinterpret_cast<const __half2*>(&g);
+            uint4 o;
+            __half2* oh = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float2 f = __half22float2(h[e]);
+                const float2 gg = __half22float2(gh[e]);
+                oh[e] = __float22half2_rn(make_float2(f.x * inv * gg.x, f.y * inv * gg.y));
+            }
+            yr[i] = o;
+        }
+    }
+}
+
+// gate <- up * gate / (1 + exp(-gate)) with the reference's mix of precisions: exp in fp32 rounded to
+// fp16, the multiply, add and divide in fp16 (gated_silu<half>, csrc/core/activation_kernel.cu:106-124).
+__device__ __forceinline__ __half2 gated_silu2(__half2 g, __half2 u)
+{
+    const float2 gf = __half22float2(g);
+    const __half2 e = __floats2half2_rn(expf(-gf.x), expf(-gf.y));
+    const __half2 one = __floats2half2_rn(1.f, 1.f);
+    return __h2div(__hmul2(u, g), __hadd2(one, e));
+}
+
+__global__ void __launch_bounds__(256)
+swiglu_kernel(__half* __restrict__ gate, const __half* __restrict__ up, size_t nvec)
+{
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= nvec) return;
+    uint4 g = reinterpret_cast<uint4*>(gate)[i];
+    const uint4 u = reinterpret_cast<const uint4*>(up)[i];
+    __half2* gh = reinterpret_cast<__half2*>(&g);
+    const __half2* uh = reinterpret_cast<const __half2*>(&u);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) gh[e] = gated_silu2(gh[e], uh[e]);
+    reinterpret_cast<uint4*>(gate)[i] = g;
+}
+
+// out += in in fp16 (add_input<half>, csrc/core/add_bias.cu:22-28).
+__global__ void __launch_bounds__(256)
+add_residual_kernel(__half* __restrict__ out, const __half* __restrict__ in, size_t nvec)
+{
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= nvec) return;
+    uint4 o = reinterpret_cast<uint4*>(out)[i];
+    const uint4 a = reinterpret_cast<const uint4*>(in)[i];
+    __half2* oh = reinterpret_cast<__half2*>(&o);
+    const __half2* ah = reinterpret_cast<const __half2*>(&a);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) oh[e] = __hadd2(oh[e], ah[e]);
+    reinterpret_cast<uint4*>(out)[i] = o;
+}
+
+// Prefill: fused projection output [B][S][3][H][D] -> Q [B][H][S][D] and K,V straight into the caches
+// [B_max][H][T_max][D] at positions 0..S-1; with rope != 0 Q and K get the NeoX rotary embedding at
+// position s (the index inside the prompt; left padding is not subtracted, as in the reference).
+// Reference: fused_QKV_neox_rotary_transpose (csrc/core/self_add_bias.cu:369-403) with the math of
+// apply_rotary_embedding (csrc/core/common.cuh:176-226) followed by copyKV_transpose
+// (csrc/core/transpose.cu:40-54); without rope, fused_QKV_transpose + copyKV_transpose as
+// BaichuanMmha::forward_full does (csrc/op/baichuan_mmha.cpp:112-137).
+__global__ void qkv_split_store_kernel(const __half* __restrict__ qkv, __half* __restrict__ q_out,
+                                       __half* __restrict__ kcache, __half* __restrict__ vcache, int S, int H, int D,
+                                       int T_max, int rope, float rope_base)
+{
+    const int s = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+    const int i = threadIdx.x;
+    const int half_d = D >> 1;
+    if (i >= half_d) return;
+    const size_t inner = (size_t)H * D;
+    const __half* src = qkv + ((size_t)b * S + s) * 3 * inner + (size_t)h * D;
+    float q1 = __half2float(src[i]), q2 = __half2float(src[i + half_d]);
+    float k1 = __half2float(src[inner + i]), k2 = __half2float(src[inner + i + half_d]);
+    const __half v1 = src[2 * inner + i], v2 = src[2 * inner + i + half_d];
+    __half oq1, oq2, ok1, ok2;
+    if (rope) {
+        const float ang = (float)s / powf(rope_base, (float)(2 * i) / (float)D);
+        const float c = cosf(ang), sn = sinf(ang);
+        oq1 = __float2half(q1 * c - q2 * sn);
+        oq2 = __float2half(q2 * c + q1 * sn);
+        ok1 = __float2half(k1 * c - k2 * sn);
+        ok2 = __float2half(k2 * c + k1 * sn);
+    }
+    else {
+        oq1 = src[i];
+        oq2 = src[i + half_d];
+        ok1 = src[inner + i];
+        ok2 = src[inner + i + half_d];
+    }
+    __half* qd = q_out + (((size_t)b * H + h) * S + s) * D;
+    qd[i] = oq1;
+    qd[i + half_d] = oq2;
+    const size_t c_off = (((size_t)b * H + h) * T_max + s) * D;
+    kcache[c_off + i] = ok1;
+    kcache[c_off + i + half_d] = ok2;
+    vcache[c_off + i] = v1;
+    vcache[c_off + i + half_d] = v2;
+}
+
+// Beam-search cache reordering: cache[b] <- cache[index[b]] for the first `step` positions
+// (reorderKV, csrc/core/transpose.cu:136-162).  The reference gathers in place and notes that the
+// read/write order is not guaranteed; here the rows are gathered into scratch first and copied back by
+// a second launch, so the result is well defined.
+__global__ void __launch_bounds__(256)
+gather_kv_kernel(const __half* __restrict__ kcache, const __half* __restrict__ vcache, const int64_t* __restrict__ index,
+                 int H, int T_max, int step, int rowvec, uint4* __restrict__ ws, size_t per_cache_vec)
+{
+    // grid: (ceil(step*rowvec/256), H, B)
+    const int b = blockIdx.z, h = blockIdx.y;
+    const int e = blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= step * rowvec) return;
+    const int src_b = (int)index[b];
+    const size_t src = (((size_t)src_b * H + h) * T_max) * rowvec + e;
+    const size_t dst = (((size_t)b * H + h) * step) * rowvec + e;
+    ws[dst] = reinterpret_cast<const uint4*>(kcache)[src];
+    ws[per_cache_vec + dst] = reinterpret_cast<const uint4*>(vcache)[src];
+}
+
+__global__ void __launch_bounds__(256)
+scatter_kv_kernel(__half* __restrict__ kcache, __half* __restrict__ vcache, int H, int T_max, int step, int rowvec,
+                  const uint4* __restrict__ ws, size_t per_cache_vec)
+{
+    const int b = blockIdx.z, h = blockIdx.y;
+    const int e = blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= step * rowvec) return;
+    const size_t dst = (((size_t)b * H + h) * T_max) * rowvec + e;
+    const size_t src = (((size_t)b * H + h) * step) * rowvec + e;
+    reinterpret_cast<uint4*>(kcache)[dst] = ws[src];
+    reinterpret_cast<uint4*>(vcache)[dst] = ws[per_cache_vec + src];
+}
+
+__global__ void advance_steps_kernel(int* steps, int count, int delta)
+{
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < count) steps[i] += delta;
+}
+
+}  // namespace
+
+int launch_rmsnorm(const __half* x, const __half* gamma, __half* y, int M, int n, float eps, cudaStream_t stream)
+{
+    EET_CHECK(n % 8 == 0 && n > 0 && n <= 16384, "rmsnorm: hidden size %d must be a multiple of 8 and <= 16384", n);
+    if (M == 0) return 0;
+    const int nv = n / 8;
+    int threads = ((nv + 1) / 2 + 31) / 32 * 32;
+    if (threads < 32) threads = 32;
+    if (threads > 1024) threads = 1024;
+    rmsnorm_kernel<<<M, threads, 0, stream>>>(x, gamma, y, n, eps);
+    EET_LAUNCH_CHECK();
+    return 0;
+}
+
+int launch_swiglu(__half* gate_inout, const __half* up, int M, int n, cudaStream_t stream)
+{
+    EET_CHECK(n % 8 == 0, "swiglu: inner size %d must be a multiple of 8", n);
+    const size_t nvec = (size_t)M * n / 8;
+    if (nvec == 0) return 0;
+    swiglu_kernel<<<(unsigned)((nvec + 255) / 256), 256, 0, stream>>>(gate_inout, up, nvec);
+    EET_LAUNCH_CHECK();
+    return 0;
+}
+
+int launch_add_residual(__half* out, const __half* in, size_t count, cudaStream_t stream)
+{
+    EET_CHECK(count % 8 == 0, "add_residual: element count must be a multiple of 8");
+    const size_t nvec = count / 8;
+    if (nvec == 0) return 0;
+    add_residual_kernel<<<(unsigned)((nvec + 255) / 256), 256, 0, stream>>>(out, in, nvec);
+    EET_LAUNCH_CHECK();
+    return 0;
+}
+
+int launch_qkv_split_store(const __half* qkv, __half* q_out, __half* kcache, __half* vcache, int B, int S, int H,
+                           int D, int T_max, int rope, float rope_base, cudaStream_t stream)
+{
+    EET_CHECK(D % 2 == 0 && D <= 2048, "qkv_split_store: head size %d unsupported", D);
+    EET_CHECK(S <= T_max, "qkv_split_store: prompt length %d exceeds the cache length %d", S, T_max);
+    EET_CHECK(H <= 65535 && B <= 65535, "qkv_split_store: head count / batch too large for the grid");
+    if (B == 0 || S == 0) return 0;
+    const int threads = (D / 2 + 31) / 32 * 32;
+    qkv_split_store_kernel<<<dim3(S, H, B), threads, 0, stream>>>(qkv, q_out, kcache, vcache, S, H, D, T_max, rope,
+                                                                 rope_base);
+    EET_LAUNCH_CHECK();
+    return 0;
+}
+
+int launch_reorder_kv(__half* kcache, __half* vcache, const int64_t* index, int B, int H, int D, int T_max, int step,
+                      __half* ws, cudaStream_t stream)
+{
+    EET_CHECK(D % 8 == 0, "reorder_kv: head size must be a multiple of 8");
+    const int rowvec = D / 8;
+    const size_t per_cache_vec = (size_t)B * H * step * rowvec;
+    dim3 grid((step * rowvec + 255) / 256, H, B);
+    gather_kv_kernel<<<grid, 256, 0, stream>>>(kcache, vcache, index, H, T_max, step, rowvec, (uint4*)ws,
+                                               per_cache_vec);
+    scatter_kv_kernel<<<grid, 256, 0, stream>>>(kcache, vcache, H, T_max, step, rowvec, (const uint4*)ws,
+                                                per_cache_vec);
+    EET_LAUNCH_CHECK();
+    return 0;
+}
+
+int launch_advance_steps(int* steps, int count, int delta, cudaStream_t stream)
+{
+    if (count <= 0) return 0;
+    advance_steps_kernel<<<(count + 127) / 128, 128, 0, stream>>>(steps, count, delta);
+    EET_LAUNCH_CHECK();
+    return 0;
+}
+
+}  // namespace eet

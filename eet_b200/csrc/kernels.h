@@ -1,0 +1,71 @@
+// Internal launcher declarations shared between the kernel files and the C ABI (api.cu).  Every
+// launcher enqueues on the given stream, allocates nothing, and returns 0 or a non-zero status after
+// recording a message with set_error().
+#pragma once
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+namespace eet {
+
+// quantize.cu
+int launch_quantize_w8(const void* w, bool fp32, int K, int N, int8_t* q_rowmajor, void* packed, void* scales,
+                       int variant, float* amax_ws, cudaStream_t stream);
+int launch_pack_w8(const int8_t* q, int K, int N, void* packed, cudaStream_t stream);
+int launch_unpack_w8(const void* packed, int K, int N, int8_t* q, cudaStream_t stream);
+int launch_repack_ref_w8(const void* ref_packed, int K, int N, void* packed, cudaStream_t stream);
+
+// gemm_skinny.cu
+struct GemmArgs {
+    const __half* A;         // [M][K]
+    const uint8_t* B;        // W8T64 [N/64][K/64][64][64]
+    const __half* scale;     // [N]
+    __half* C;               // [M][N]
+    const __half* residual;  // [M][N] or null; added in fp16 after the product was rounded to fp16
+    const uint8_t* B2;       // second weight (SwiGLU "up") or null
+    const __half* scale2;
+    int M, N, K;
+    int epilogue;            // 0 plain, 1 + residual, 2 silu(A.B) * (A.B2)
+    float* ws;               // split-K accumulation scratch (zero on entry, left zero on exit)
+    size_t ws_bytes;
+};
+size_t skinny_workspace_bytes(int M, int N, int dual);
+int launch_gemm_skinny(const GemmArgs& a, cudaStream_t stream);
+
+// gemm_tc.cu (tcgen05 / TMEM)
+int launch_gemm_tc(const GemmArgs& a, cudaStream_t stream);
+
+// glue.cu
+int launch_rmsnorm(const __half* x, const __half* gamma, __half* y, int M, int n, float eps, cudaStream_t stream);
+int launch_swiglu(__half* gate_inout, const __half* up, int M, int n, cudaStream_t stream);
+int launch_add_residual(__half* out, const __half* in, size_t count, cudaStream_t stream);
+int launch_qkv_split_store(const __half* qkv, __half* q_out, __half* kcache, __half* vcache, int B, int S, int H,
+                           int D, int T_max, int rope, float rope_base, cudaStream_t stream);
+int launch_reorder_kv(__half* kcache, __half* vcache, const int64_t* index, int B, int H, int D, int T_max, int step,
+                      __half* ws, cudaStream_t stream);
+int launch_advance_steps(int* steps, int count, int delta, cudaStream_t stream);
+
+// attention.cu
+struct DecodeAttnArgs {
+    const __half* qkv;        // [B][3][H][D] fused projection output of the new token
+    __half* kcache;           // [B_max][H][T_max][D]
+    __half* vcache;
+    __half* ctx;              // [B][H*D]
+    int B, H, D, T_max;
+    int step;                 // history length including the new token (used when step_dev is null)
+    const int* step_dev;      // optional device-resident step
+    const int64_t* pad_len;   // [B] or null
+    const __half* alibi;      // [H][alibi_stride] bias row for the newest position, or null
+    int alibi_stride;
+    const float* alibi_slopes;  // [H] or null: bias = fp16(slope * t), the closed form of the same row
+    int rope;                 // 1: rotate q,k (NeoX pairing) at position step-1
+    float rope_base;
+    int splits;               // CTAs per (batch, head): 1, 2, 4 or 8; 0 = choose
+};
+int launch_decode_mha(const DecodeAttnArgs& a, cudaStream_t stream);
+int launch_prefill_mha(const __half* q, const __half* kcache, const __half* vcache, __half* ctx, int B, int S, int H,
+                       int D, int T_max, const int64_t* pad_len, const __half* alibi, int alibi_stride,
+                       cudaStream_t stream);
+
+}  // namespace eet

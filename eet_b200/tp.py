@@ -1,0 +1,73 @@
+"""Tensor parallelism for the int8 LLaMA / Baichuan path: Megatron-style sharding with one all-reduce
+per row-parallel projection.  The reference is single-GPU (it has no communication layer at all); this
+module is an addition on top of its operator API.
+
+One process per GPU.  Column-parallel: fused QKV (by heads), gate and up (by d_ff).  Row-parallel: the
+attention output projection and the FFN down projection; their partial outputs are summed over the group
+and the residual is added after the sum.  RMSNorm weights, embedding and lm_head are replicated.
+"""
+import os
+
+import torch
+import torch.distributed as dist
+
+
+class TensorParallel:
+    """Handle passed to MetaDesc(tp=...).  Wraps a torch.distributed process group (NCCL on GPUs, gloo in
+    CPU tests)."""
+
+    def __init__(self, group=None):
+        if not dist.is_initialized():
+            raise RuntimeError("torch.distributed is not initialised")
+        self.group = group
+        self.rank = dist.get_rank(group)
+        self.size = dist.get_world_size(group)
+
+    def all_reduce(self, tensor):
+        """In-place sum over the group on the current stream."""
+        if self.size > 1:
+            dist.all_reduce(tensor, op=dist.ReduceOp.SUM, group=self.group)
+        return tensor
+
+
+def init_from_env(backend="nccl"):
+    """Initialises torch.distributed from the torchrun environment (RANK, WORLD_SIZE, LOCAL_RANK,
+    MASTER_ADDR, MASTER_PORT), binds this process to its GPU and returns a TensorParallel over the world
+    group; returns None when WORLD_SIZE is 1 or unset."""
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world <= 1:
+        return None
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if backend == "nccl":
+        torch.cuda.set_device(local_rank)
+    if not dist.is_initialized():
+        kwargs = {}
+        if backend == "nccl":
+            kwargs["device_id"] = torch.device("cuda", local_rank)
+        dist.init_process_group(backend=backend, **kwargs)
+    return TensorParallel()
+
+
+def head_range(num_heads, rank, size):
+    """Heads [lo, hi) owned by `rank`: attention shards by whole heads, equally."""
+    if num_heads % size:
+        raise ValueError(f"{num_heads} heads do not divide over {size} ranks")
+    per = num_heads // size
+    return rank * per, (rank + 1) * per
+
+
+def ff_range(d_ff, rank, size):
+    """FFN inner channels [lo, hi) owned by `rank`.  The packed weight layout works in tiles of 64
+    channels, so the split is by tiles and may be uneven: LLaMA-7B's 11008 = 172 tiles over 8 ranks gives
+    shards of 21 or 22 tiles."""
+    if d_ff % 64:
+        raise ValueError(f"d_ff {d_ff} must be a multiple of 64")
+    tiles = d_ff // 64
+    if tiles < size:
+        raise ValueError(f"d_ff {d_ff} has fewer 64-channel tiles than the {size} ranks")
+    return 64 * (tiles * rank // size), 64 * (tiles * (rank + 1) // size)
+
+
+def shard_plan(num_heads, d_ff, size):
+    """Per-rank (head range, ffn range) for a tensor-parallel degree; raises if it cannot be sharded."""
+    return [(head_range(num_heads, r, size), ff_range(d_ff, r, size)) for r in range(size)]

@@ -1,0 +1,168 @@
+/*
+ * eet_b200 - C ABI of the B200 (sm_100a) int8 weight-only inference path.
+ *
+ * Every entry point takes plain pointers and sizes; device pointers are raw CUDA device addresses owned
+ * by the caller, `stream` is a cudaStream_t passed as void*.  Every function enqueues its work on
+ * `stream` and returns immediately: 0 on success, non-zero on failure, in which case eet_last_error()
+ * returns a message.  The library allocates no device memory; kernels that need scratch take it from
+ * the caller, sized by the matching *_workspace_bytes() function.
+ *
+ * Each declaration names the interface of the reference project (NetEase-FuXi/EET, paths inside that
+ * project) that it stands in for.
+ */
+#ifndef EET_B200_H
+#define EET_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ABI version of this header; bumped when a signature changes. */
+int eet_abi_version(void);
+
+/* Message of the last failure on the calling thread ("" if none). */
+const char* eet_last_error(void);
+
+/* Reads (and clears) the device-side status word of the current device: 0 = no kernel gave up on a
+ * bounded wait since the last call.  Synchronises the device. */
+int eet_device_status(int* status_out);
+
+/* ------------------------------------------------------------------------------------------------
+ * Quantizer and packer
+ * ---------------------------------------------------------------------------------------------- */
+
+/* Scratch needed by eet_quantize_w8: N floats. */
+size_t eet_quantize_w8_workspace_bytes(int K, int N);
+
+/*
+ * Symmetric per-output-channel int8 quantization of a row-major weight W[K][N] (K = reduction dim),
+ * bit-exact with the reference.
+ * Replaces: fastertransformer::symmetric_quantize<half,half> / <float,float>
+ *           (3rdparty/cutlass_kernels/cutlass_preprocessors.cc:581-678) as reached through
+ *           symmetric_quantize_last_axis_of_tensor (3rdparty/cutlass_kernels/fpA_intB_gemm_wrapper.cu:27-105,
+ *           Python name EET.quant_weights, csrc/py11/eet2py.cpp:152-155).
+ *   w            device, fp16 (w_is_fp32 = 0) or fp32 (1), K % 64 == 0, N % 64 == 0
+ *   q_rowmajor   device int8 [K][N], the "unprocessed" tensor; may be NULL
+ *   packed       device, K*N bytes in the W8T64 layout consumed by eet_gemm_w8a16
+ *   scales       device [N], fp16 when w is fp16, fp32 when w is fp32
+ *   variant      0 = reference (amax/128, clip [-128,127]); 1 = amax/127, clip [-127,127]
+ *   ws           device scratch of eet_quantize_w8_workspace_bytes(K, N) bytes
+ */
+int eet_quantize_w8(const void* w, int w_is_fp32, int K, int N, int8_t* q_rowmajor, void* packed, void* scales,
+                    int variant, void* ws, size_t ws_bytes, void* stream);
+
+/*
+ * Row-major int8 [K][N] -> W8T64 bytes.
+ * Replaces: fastertransformer::preprocess_weights (cutlass_preprocessors.cc:536-544; Python name
+ *           EET.preprocess_weights, csrc/py11/eet2py.cpp:148-150, wrapper fpA_intB_gemm_wrapper.cu:107-126).
+ */
+int eet_pack_w8(const int8_t* q_rowmajor, int K, int N, void* packed, void* stream);
+
+/* W8T64 bytes -> row-major int8 [K][N] (no counterpart in the reference; used to re-shard packed
+ * weights for tensor parallelism and in tests). */
+int eet_unpack_w8(const void* packed, int K, int N, int8_t* q_rowmajor, void* stream);
+
+/* Bytes packed by the reference for sm75-89 (preprocess_weights_for_mixed_gemm,
+ * cutlass_preprocessors.cc:497-534) -> W8T64, so checkpoints converted by the reference load unchanged. */
+int eet_repack_ref_w8(const void* ref_packed, int K, int N, void* packed, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * W8A16 GEMM
+ * ---------------------------------------------------------------------------------------------- */
+
+/* Scratch needed by eet_gemm_w8a16 for a problem of this size.  The scratch must be zero before its
+ * first use (e.g. cudaMemset once after allocation); every call leaves it zero again.  Calls that share
+ * one scratch buffer must not overlap on the GPU. */
+size_t eet_gemm_w8a16_workspace_bytes(int M, int N, int K);
+
+/*
+ * C[M][N] (fp16) = A[M][K] (fp16, row-major) x dequant(B), B = W8T64 bytes of a [K][N] int8 matrix,
+ * scale fp16 [N].
+ * Replaces: fastertransformer::gemm_fp16_int_bias_act<uint8_t>
+ *           (3rdparty/cutlass_kernels/fpA_intB_gemm.cu:36-62 -> CutlassFpAIntBGemmRunner::gemm,
+ *           fpA_intB_gemm/fpA_intB_gemm_template.h:545-558) as called from
+ *           csrc/op/llama_mmha.cpp:313-337,428-447 and csrc/op/gated_ffn_int8.cpp:253-326.
+ *   epilogue  0: C = A.B;  1: C = fp16(A.B) + residual in fp16, the add_input kernel that follows the
+ *             projection GEMMs in the reference (csrc/core/add_bias.cu:22-28) fused in.
+ *   residual  device fp16 [M][N] for epilogue 1, else NULL (may alias C)
+ * M may be any value >= 0; K and N must be multiples of 64; pointers 16-byte aligned.
+ */
+int eet_gemm_w8a16(const void* A, const void* packedB, const void* scale, void* C, int M, int N, int K,
+                   const void* residual, int epilogue, void* ws, size_t ws_bytes, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Kernels between the GEMMs
+ * ---------------------------------------------------------------------------------------------- */
+
+/* y = x * rsqrt(mean(x^2) + eps) * gamma over rows of length n.
+ * Replaces: RMSnorm<half> (csrc/core/layer_norm.cu:580-625 -> T5norm1_kernel_opt :490-531). */
+int eet_rmsnorm(const void* x, const void* gamma, void* y, int M, int n, float eps, void* stream);
+
+/* gate <- up * silu(gate), in place.  Replaces: gated_act_kernel<half> with act_type silu
+ * (csrc/core/activation_kernel.cu:275-338 -> gated_silu :106-124). */
+int eet_swiglu(void* gate_inout, const void* up, int M, int n, void* stream);
+
+/* out += in (fp16), `count` elements.  Replaces: add_bias_input_kernel<half> with a null bias
+ * (csrc/core/add_bias.cu:51-73 -> add_input :22-28). */
+int eet_add_residual(void* out, const void* in, size_t count, void* stream);
+
+/*
+ * Prefill: fused projection output qkv[B][S][3][H][D] -> q_out[B][H][S][D], and K, V written into the
+ * caches [B_max][H][T_max][D] at positions 0..S-1; rope != 0 applies the NeoX rotary embedding
+ * (base rope_base) to q and k at position s.
+ * Replaces: fused_QKV_bias_rotary_kernel<half> (csrc/core/self_add_bias.cu:442-487 -> :369-403) or, with
+ *           rope = 0, fused_add_QKV_bias_kernel without bias, followed by copyKV_transpose_kernel
+ *           (csrc/core/transpose.cu:116-124).
+ */
+int eet_qkv_split_store(const void* qkv, void* q_out, void* kcache, void* vcache, int B, int S, int H, int D,
+                        int T_max, int rope, float rope_base, void* stream);
+
+/*
+ * Prefill causal self-attention over the freshly stored cache: ctx[B][S][H*D].
+ * pad_len: device int64 [B] left-padding lengths or NULL; alibi: device fp16 [H][S][S] bias
+ * (alibi_stride = S) or NULL.
+ * Replaces: q_k_mul + qk_softmax + attn_v_mul + transpose of LlamaMmha::forward_full /
+ *           BaichuanMmha::forward_full (csrc/op/llama_mmha.cpp:354-426, csrc/op/baichuan_mmha.cpp:117-150;
+ *           softmax kernels csrc/core/gpt2_self_softmax.cu:8-57,161-240).
+ */
+int eet_prefill_mha(const void* q, const void* kcache, const void* vcache, void* ctx, int B, int S, int H, int D,
+                    int T_max, const int64_t* pad_len, const void* alibi, int alibi_stride, void* stream);
+
+/*
+ * One decode step of masked multi-head attention for every (batch, head): rotates the new q,k
+ * (rope != 0), appends k,v to the caches at position step-1 and attends over positions
+ * [pad_len[b], step).  qkv[B][3][H][D] is the fused projection of the new token; ctx[B][H*D].
+ *   step        history length including the new token, used when step_dev is NULL
+ *   step_dev    optional device int32 holding the same number (lets a captured CUDA graph be replayed
+ *               while the step advances on the device, see eet_advance_steps)
+ *   alibi       device fp16 [H][alibi_stride] bias for the newest row (what the reference's Python
+ *               passes as alibi_mask[:, -1:, :]) or NULL;  alibi_slopes: device fp32 [H] or NULL, the
+ *               closed form of the same row: bias[h][t] = fp16(slope[h] * t)
+ *   splits      CTAs cooperating on one (batch, head): 0 = choose, else 1, 2, 4 or 8
+ * Replaces: masked_attention_dispatch<half> (csrc/core/attention_dispatch.cu:888-928 -> :140-324),
+ *           fused_masked_attention_dispatch<half> (:1338-1426 -> :1155-1336) and the decode call of
+ *           fused_QKV_bias_rotary_kernel (csrc/op/llama_mmha.cpp:241).
+ */
+int eet_decode_mha(const void* qkv, void* kcache, void* vcache, void* ctx, int B, int H, int D, int T_max, int step,
+                   const int* step_dev, const int64_t* pad_len, const void* alibi, int alibi_stride,
+                   const float* alibi_slopes, int rope, float rope_base, int splits, void* stream);
+
+/* Scratch needed by eet_reorder_kv: 2 * B * H * step * D halves. */
+size_t eet_reorder_kv_workspace_bytes(int B, int H, int D, int step);
+
+/* Beam search: cache[b] <- cache[index[b]] for positions [0, step).  index: device int64 [B].
+ * Replaces: reorderKV_kernel<half> (csrc/core/transpose.cu:136-162). */
+int eet_reorder_kv(void* kcache, void* vcache, const int64_t* index, int B, int H, int D, int T_max, int step,
+                   void* ws, size_t ws_bytes, void* stream);
+
+/* steps[i] += delta for i < count (device int32).  The reference keeps its step counter on the host
+ * (LlamaMmha::step_, csrc/op/llama_mmha.cpp:121,195,210); this is its device-resident twin. */
+int eet_advance_steps(int* steps, int count, int delta, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* EET_B200_H */

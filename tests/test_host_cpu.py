@@ -1,0 +1,59 @@
+"""Host-side logic that needs no GPU: descriptor validation, quantizer input checks, weight-dictionary
+conversion rules, tensor-parallel shard plans."""
+import pytest
+import torch
+
+from eet_b200 import EET, tp
+from eet_b200.modeling import convert_name, gen_alibi_mask
+
+
+def test_metadesc_validation():
+    d = EET.MetaDesc(dtype=torch.float16, batch_size=2, head_num=2, hidden_units=256, layer_num=1, max_seq_len=8,
+                     max_full_seq_len=16, activation_fn="silu", d_ff=512, cuda_device="cuda:0", layernorm_eps=1e-6,
+                     is_int8=True)
+    assert d.max_full_seq_len == 16 and d.is_int8
+    with pytest.raises(RuntimeError):
+        EET.MetaDesc(torch.float16, 0, 2, 256, 1, 8)
+    with pytest.raises(RuntimeError):
+        EET.MetaDesc(torch.float16, 1, 2, 256, 1, 8, cuda_device="cpu")
+    with pytest.raises(RuntimeError):
+        EET.MetaDesc(torch.float16, 1, 2, 256, 1, 8, requires_grad=True)
+
+
+def test_quant_weights_rejects_what_the_reference_rejects():
+    with pytest.raises(RuntimeError, match="contiguous"):
+        EET.quant_weights(torch.zeros(64, 128).t(), torch.int8)
+    with pytest.raises(RuntimeError, match="empty"):
+        EET.quant_weights(torch.zeros(0, 64), torch.int8)
+    with pytest.raises(RuntimeError, match="dim"):
+        EET.quant_weights(torch.zeros(64), torch.int8)
+    with pytest.raises(RuntimeError, match="FP16 or FP32"):
+        EET.quant_weights(torch.zeros(64, 64, dtype=torch.float64), torch.int8)
+    with pytest.raises(RuntimeError, match="int8"):
+        EET.quant_weights(torch.zeros(64, 64), torch.float16)
+
+
+def test_convert_name_rules():
+    assert convert_name("layers.0.mlp.down_proj.weight") == "layer.0.ffn.output.weight"
+    assert convert_name("layers.7.self_attn.qkv_proj.weight") == "layer.7.self_attn.qkv_proj.weight"
+    with pytest.raises(KeyError):
+        convert_name("layers.0.x", "gpt2")
+
+
+def test_shard_plan():
+    plan = tp.shard_plan(32, 11008, 2)
+    assert plan == [((0, 16), (0, 5504)), ((16, 32), (5504, 11008))]
+    # 172 tiles of 64 over 8 ranks: uneven, contiguous, complete
+    plan8 = tp.shard_plan(32, 11008, 8)
+    widths = [hi - lo for _, (lo, hi) in plan8]
+    assert sum(widths) == 11008 and set(widths) == {21 * 64, 22 * 64}
+    assert all(plan8[i][1][1] == plan8[i + 1][1][0] for i in range(7))
+    with pytest.raises(ValueError):
+        tp.shard_plan(32, 11008, 3)     # heads do not divide
+    with pytest.raises(ValueError):
+        tp.ff_range(128, 0, 4)          # fewer tiles than ranks
+
+
+def test_alibi_mask_shape():
+    m = gen_alibi_mask(8, 5)
+    assert m.shape == (8, 5, 5) and torch.isinf(m[0, 0, 1]) and m[0, 4, 0] == 0
