@@ -1,0 +1,422 @@
+"""Benchmark of the int8 weight-only LLaMA-7B-architecture decode path (BASELINE.json configs[2]) plus
+the W8A16 GEMM sweep of configs[1].
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+A "step" is one greedy decode step of the whole batch (B = 8 sequences, prompt 512, random-init weights
+quantized to int8 on the fly, synthetic token ids).  Rank 0 prints ONE JSON line:
+
+  value      tokens/s over K timed decode steps with the token ids already on the device (CUDA events)
+  e2e        tokens/s through the public model API with the ids coming from pinned host memory and the
+             chosen tokens read back to the host every step
+  roofline   the W8A16 skinny GEMM (dominant kernel): algorithmic bytes / measured kernel time vs the
+             measured HBM copy bandwidth
+  gemm_sweep GB/s and TFLOP/s of the GEMM for the LLaMA-7B projection shapes over M (N = 1 only)
+  cpu_baseline  the CPU oracle (a port of the reference's arithmetic; the reference has no CPU path) on a
+             bounded sample, on this host's cores
+
+`--impl reference` times that CPU port alone and prints the same line shape with "impl": "reference".
+For N > 1 launch with torchrun; the model is sharded Megatron-style (strong scaling).
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+import types
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+METRIC = "int8_llama7b_decode_tokens_per_s"
+UNIT = "tokens/s"
+CFG = dict(hidden_size=4096, num_attention_heads=32, num_hidden_layers=32, intermediate_size=11008, vocab_size=32000,
+           rms_norm_eps=1e-6, hidden_act="silu", pad_token_id=None)
+BATCH, PROMPT = 8, 512
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return {"hbm_gbs": float(p["hbm_gbs"]), "tflops": float(p["bf16_tflops"]), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "tflops": 1590.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while a timed region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+            self.thread.join(timeout=2)
+
+    def summary(self):
+        mhz, mx, reasons = [], 0, set()
+        for r in self.rows:
+            if len(r) < 6:
+                continue
+            try:
+                mhz.append(float(r[0]))
+                mx = max(mx, float(r[1]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(mhz) if mhz else None, "sm_max_mhz": mx or None,
+                "reasons": sorted(reasons), "samples": len(mhz)}
+
+
+# ------------------------------------------------------------------------------------------------ model
+def build_model(tp, device_index, t_max, layers=None):
+    """Random-init LLaMA-7B-architecture weights (N(0, 0.02^2), fp16) generated on the GPU, quantized by the
+    library's quantizer, and assembled through the public from_eet() entry point.  Every rank draws the same
+    full matrices (same seed) and keeps its shard."""
+    from eet_b200 import EET, modeling
+    cfg = types.SimpleNamespace(**CFG)
+    if layers:
+        cfg.num_hidden_layers = layers
+    dev = torch.device("cuda", device_index)
+    gen = torch.Generator(device=dev).manual_seed(0)
+    h, f, v = cfg.hidden_size, cfg.intermediate_size, cfg.vocab_size
+
+    def qw(k, n):
+        w = (torch.randn(n, k, generator=gen, device=dev, dtype=torch.float32) * 0.02).half().t().contiguous()
+        return EET.quant_weights(w, torch.int8, False)
+
+    d = {"embed_tokens.weight": (torch.randn(v, h, generator=gen, device=dev) * 0.02).half(),
+         "norm.weight": torch.ones(h, device=dev).half(),
+         "lm_head.weight": (torch.randn(v, h, generator=gen, device=dev) * 0.02).half()}
+    for i in range(cfg.num_hidden_layers):
+        p = f"layer.{i}."
+        for name, (k, n) in (("self_attn.qkv_proj", (h, 3 * h)), ("self_attn.out_proj", (h, h)),
+                             ("ffn.intermediate_0", (h, f)), ("ffn.intermediate_1", (h, f)), ("ffn.output", (f, h))):
+            d[p + name + ".weight"], d[p + name + ".scale"] = qw(k, n)
+        d[p + "self_attn.layernorm.weight"] = torch.ones(h, device=dev).half()
+        d[p + "ffn.layernorm.weight"] = torch.ones(h, device=dev).half()
+    model = modeling.EETLlamaForCausalLM.from_eet(d, cfg, BATCH, PROMPT, t_max, torch.int8, device_id=device_index,
+                                                  tp=tp)
+    return model, cfg
+
+
+def rewind(model, step):
+    """Puts every attention op back to a history of `step` tokens (the cache contents beyond it are simply
+    overwritten again); used to time two regions over the same range of cache lengths."""
+    model.end_graph()
+    model.model.past_kv_length = step
+    for layer in model.model.layers:
+        layer.attention.step_ = step
+
+
+def kernel_launches_per_step(n_layers):
+    # per layer: rmsnorm, qkv gemm, decode attention, out gemm, rmsnorm, gate gemm, up gemm, swiglu, down gemm
+    # per step: advance_steps + final rmsnorm
+    return 9 * n_layers + 2
+
+
+# ------------------------------------------------------------------------------------------------ GEMM timing
+def _time_graph(fn, iters_in_graph, reps=5):
+    """Captures `fn` (which enqueues iters_in_graph launches) into a CUDA graph and returns the best time per
+    launch over `reps` replays: kernel time without the host cost of a Python/ctypes launch."""
+    fn()  # eager once: sizes pooled scratch, sets function attributes
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        fn()
+    best = None
+    for _ in range(reps + 1):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        g.replay()
+        e1.record()
+        e1.synchronize()
+        t = e0.elapsed_time(e1) * 1e-3 / iters_in_graph
+        best = t if best is None else min(best, t)
+    return best
+
+
+def time_gemm_shapes(model, batch):
+    """Times the skinny GEMM alone on the real weights of the model: for each of the five projection shapes,
+    all layers' launches back to back inside one CUDA graph between two CUDA events (one distinct weight
+    buffer per layer, GBs in total, so nothing is served from L2).  Returns per-shape results."""
+    from eet_b200 import EET
+    dev = model.model.desc.device
+    per = {}
+    layers = model.model.layers
+    shapes = (("qkv", "qkv_w", "qkv_s"), ("out", "out_w", "out_s"), ("gate", "w0", "s0"), ("up", "w1", "s1"),
+              ("down", "w2", "s2"))
+    for name, wn, sn in shapes:
+        K, N = getattr(layers[0], wn).shape
+        x = torch.randn(batch, K, device=dev).half()
+        out = torch.empty(batch, N, device=dev, dtype=torch.float16)
+
+        def run():
+            for layer in layers:
+                EET.gemm_w8a16(x, getattr(layer, wn), getattr(layer, sn), out=out)
+
+        t = _time_graph(run, len(layers))
+        nbytes = N * K + 2 * N + 2 * batch * K + 2 * batch * N
+        per[name] = {"K": K, "N": N, "M": batch, "us": t * 1e6, "bytes": nbytes, "gbs": nbytes / t / 1e9}
+    return per
+
+
+def gemm_sweep(device, hbm_peak, tflops_peak):
+    """configs[1]: K x N in {4096x4096, 4096x11008, 11008x4096}, M in {1..4096}; 8 rotating weight buffers
+    (134-360 MB per shape, more than the 126 MB L2), launches replayed from a CUDA graph."""
+    from eet_b200 import EET
+    res = []
+    for K, N in ((4096, 4096), (4096, 11008), (11008, 4096)):
+        nbuf = 8
+        ws = [torch.randint(-128, 128, (K, N), dtype=torch.int8, device=device) for _ in range(nbuf)]
+        s = (torch.rand(N, device=device) * 1e-3).half()
+        for M in (1, 2, 4, 8, 16, 64, 256, 1024, 4096):
+            x = torch.randn(M, K, device=device).half()
+            out = torch.empty(M, N, device=device, dtype=torch.float16)
+            iters = 32 if M <= 64 else 8
+
+            def run():
+                for i in range(iters):
+                    EET.gemm_w8a16(x, ws[i % nbuf], s, out=out)
+
+            t = _time_graph(run, iters, reps=3)
+            nbytes = N * K + 2 * N + 2 * M * K + 2 * M * N
+            flops = 2.0 * M * N * K
+            t_roof = max(nbytes / (hbm_peak * 1e9), flops / (tflops_peak * 1e12))
+            res.append({"K": K, "N": N, "M": M, "us": round(t * 1e6, 2), "gbs": round(nbytes / t / 1e9, 1),
+                        "tflops": round(flops / t / 1e12, 2), "frac_of_roofline": round(t_roof / t, 4)})
+        del ws
+    return res
+
+
+# ------------------------------------------------------------------------------------------------ CPU port
+def cpu_decode_sample(steps, layers=1, threads=None):
+    """Times the CPU oracle on a bounded sample of the workload: `steps` decode steps of the first `layers`
+    layers of the LLaMA-7B architecture at batch 8 with 512 tokens of history, fp32 torch ops on all host
+    cores.  Returns (tokens/s extrapolated to 32 layers, cores, description)."""
+    from oracle import ops
+    threads = threads or os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    cfg = types.SimpleNamespace(**CFG)
+    h, f, H, D = cfg.hidden_size, cfg.intermediate_size, cfg.num_attention_heads, 128
+    gen = torch.Generator().manual_seed(0)
+
+    def qw(k, n):
+        q = torch.randint(-128, 128, (k, n), generator=gen, dtype=torch.int8)
+        return q, (torch.rand(n, generator=gen) * 3e-4 + 1e-4).half()
+
+    lw = []
+    for _ in range(layers):
+        args = []
+        for k, n in ((h, 3 * h), (h, h), (h, f), (h, f), (f, h)):
+            args.extend(qw(k, n))
+        lw.append(ops.LayerWeights(*args, torch.ones(h).half(), torch.ones(h).half()))
+    dec = ops.DecoderOracle(lw, H, D, cfg.rms_norm_eps, PROMPT + steps + 2, BATCH)
+    for c in dec.kc + dec.vc:
+        c[:, :, :PROMPT] = torch.randn(BATCH, H, PROMPT, D, generator=gen).half()
+    dec.step = PROMPT
+    x = torch.randn(BATCH, 1, h, generator=gen).half()
+    dec.forward(x, False)  # warm-up
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        dec.forward(x, False)
+    dt = (time.perf_counter() - t0) / steps
+    tok_s = BATCH / (dt * cfg.num_hidden_layers / layers)
+    sample = (f"{steps} decode steps of {layers} of 32 layers (batch {BATCH}, history {PROMPT}), time scaled by "
+              f"32/{layers}; torch fp32 ops on {threads} threads")
+    return tok_s, threads, sample, dt
+
+
+# ------------------------------------------------------------------------------------------------ arms
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    t0 = time.perf_counter()
+    steps = max(1, min(args.steps, 16))
+    tok_s, threads, sample, dt = cpu_decode_sample(steps)
+    line = {"impl": "reference", "metric": METRIC, "value": round(tok_s, 3), "unit": UNIT, "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(dt * 32 * 1e3, 3),
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32 (cpu port of f16 path)",
+            "data": "synthetic",
+            "config": {"workload": "llama7b_arch_int8_decode_b8_prompt512", "global_batch": BATCH, "seq_len": PROMPT},
+            "cpu_baseline": {"value": round(tok_s, 3), "unit": UNIT, "cores": threads, "kind": "port",
+                             "sample": sample},
+            "e2e": {"value": round(tok_s, 3), "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "note": "the reference has no CPU implementation of this path and its GPU kernels refuse sm_90+; this "
+                    "arm times the CPU restatement (oracle/ops.py) of the reference's arithmetic",
+            "wall_s": round(time.perf_counter() - t0, 1)}
+    print(json.dumps(line))
+
+
+def run_ours(args):
+    from eet_b200 import tp as tp_mod
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    tp = tp_mod.init_from_env("nccl") if world > 1 else None
+    dev = torch.device("cuda", local)
+    K, W = args.steps, args.warmup
+    t_max = PROMPT + W + K + 4
+    model, cfg = build_model(tp, local, t_max, layers=args.layers)
+    n_layers = cfg.num_hidden_layers
+    model.use_cuda_graph = not args.no_graph
+
+    gen = torch.Generator().manual_seed(1)
+    prompt = torch.randint(0, cfg.vocab_size, (BATCH, PROMPT), generator=gen)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(x):
+        if world == 1:
+            return x
+        t = torch.tensor([x], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # prefill (untimed set-up of the 512-token history)
+    if args.skip_prefill:
+        for layer in model.model.layers:   # profiling runs: a random history instead of a real prefill
+            layer.attention.k_cache.normal_()
+            layer.attention.v_cache.normal_()
+        rewind(model, PROMPT)
+        first = prompt[:, -1:].to(dev)
+    else:
+        out = model(prompt.to(dev), first_pass=True)
+        first = torch.argmax(out.logits[:, -1, :], dim=-1, keepdim=True)
+        del out
+    torch.cuda.synchronize()
+
+    host_ids = torch.empty((BATCH, 1), dtype=torch.long).pin_memory()
+    host_next = torch.empty((BATCH, 1), dtype=torch.long).pin_memory()
+
+    # ---- region 1: end to end through the public API, ids from pinned host memory, tokens read back ----
+    host_ids.copy_(first.cpu())
+    for _ in range(W):
+        nxt = model.decode_step(host_ids.to(dev, non_blocking=True))
+        host_next.copy_(nxt, non_blocking=True)
+        torch.cuda.synchronize()
+        host_ids.copy_(host_next)
+    barrier()
+    with ClockSampler(local) as clk_e2e:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(K):
+            nxt = model.decode_step(host_ids.to(dev, non_blocking=True))
+            host_next.copy_(nxt, non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+            host_ids.copy_(host_next)
+        e1.record()
+        barrier()
+    t_e2e = max_over_ranks(e0.elapsed_time(e1) * 1e-3)
+
+    # ---- region 2: same range of cache lengths, ids resident on the device ----
+    rewind(model, PROMPT)
+    ids = first.clone()
+    for _ in range(W):
+        ids = model.decode_step(ids).clone()
+    barrier()
+    with ClockSampler(local) as clk:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(K):
+            ids = model.decode_step(ids)
+        e1.record()
+        barrier()
+    t_dev = max_over_ranks(e0.elapsed_time(e1) * 1e-3)
+
+    from eet_b200 import _lib
+    status = _lib.device_status()
+
+    pk = peaks()
+    gemms = time_gemm_shapes(model, BATCH)
+    g_bytes = sum(v["bytes"] for v in gemms.values())
+    g_time = sum(v["us"] for v in gemms.values()) * 1e-6
+    achieved = g_bytes / g_time / 1e9
+    line = {"metric": METRIC, "value": round(BATCH * K / t_dev, 2), "unit": UNIT, "n_gpus": world, "steps": K,
+            "warmup": W, "ms_per_step": round(t_dev / K * 1e3, 4), "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f16 activations x int8 weights, f32 accumulate", "data": "synthetic",
+            "config": {"workload": "llama7b_arch_int8_decode_b8_prompt512", "layers": n_layers, "global_batch": BATCH,
+                       "seq_len": PROMPT, "cache_len_during_timing": [PROMPT + W + 1, PROMPT + W + K],
+                       "parallelism": f"tp{world}", "cuda_graph": model.use_cuda_graph,
+                       "l2": "weights (6.5 GB per step) and KV cache exceed L2; no flush needed"},
+            "e2e": {"value": round(BATCH * K / t_e2e, 2), "unit": UNIT, "h2d_bytes_per_step": BATCH * 8,
+                    "d2h_bytes_per_step": BATCH * 8, "ms_per_step": round(t_e2e / K * 1e3, 4)},
+            "gpu_launches": kernel_launches_per_step(n_layers) * K,
+            "clocks": clk.summary(), "clocks_e2e": clk_e2e.summary(), "device_status": status,
+            "roofline": {"bound": "hbm", "kernel": "gemm_skinny_kernel<8> (5 projection shapes x layers, M=8)",
+                         "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                         "frac": round(achieved / pk["hbm_gbs"], 4), "peak_source": pk["source"], "traffic": None,
+                         "per_shape": {k: {"K": v["K"], "N": v["N"], "us": round(v["us"], 2), "gbs": round(v["gbs"], 1)}
+                                       for k, v in gemms.items()}}}
+    if world == 1 and not args.no_sweep:
+        line["gemm_sweep"] = gemm_sweep(dev, pk["hbm_gbs"], pk["tflops"])
+    if rank == 0 and world == 1 and not args.no_cpu:
+        tok_s, threads, sample, _ = cpu_decode_sample(8)
+        line["cpu_baseline"] = {"value": round(tok_s, 3), "unit": UNIT, "cores": threads, "kind": "port",
+                                "sample": sample}
+    if rank == 0:
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=None, help="fewer layers than 32 (profiling runs only)")
+    ap.add_argument("--no-graph", action="store_true", help="launch the decode step eagerly")
+    ap.add_argument("--no-sweep", action="store_true", help="skip the GEMM sweep")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline")
+    ap.add_argument("--skip-prefill", action="store_true",
+                    help="fill the KV cache with random data instead of running the prompt (profiling runs only)")
+    args = ap.parse_args()
+    if args.warmup < 3:
+        args.warmup = 3
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -14,9 +14,10 @@
 //    cp.async.bulk + mbarrier complete_tx): up to 32 KiB of weights plus the matching slice of the
 //    activations per stage, 4-5 stages in flight per SM.
 //  * Eight consumer warps each take one 64x64 tile of a stage: 16-byte shared loads deliver exactly the
-//    B fragments of mma.m16n8k16 (8 channels x 64 reduction indices per load), bytes become fp16 in
-//    registers (prmt + sub.f16x2) and feed the tensor cores with the activations as the A operand; the
-//    reduction index is permuted identically on both operands, so no shuffles or transposes are needed.
+//    A fragments of mma.m16n8k16 (16 channels x 64 reduction indices per pair of loads), bytes become
+//    fp16 in registers (prmt + sub.f16x2) and feed the tensor cores with up to 8 tokens as the B operand;
+//    the reduction index is permuted identically on both operands, so no shuffles or transposes are
+//    needed.
 //  * When a CTA's run ends inside a tile row, partial sums go to an fp32 scratch with red.global.add and
 //    a per-tile-row arrival counter; the CTA that completes the count applies the scale (and residual),
 //    writes fp16, and restores the scratch to zero.  Tile rows covered by one CTA skip the scratch.
@@ -38,6 +39,7 @@ constexpr int kStageTiles = 8;                       // W8T64 tiles per stage
 constexpr int kStageWBytes = kStageTiles * kTileBytes;
 constexpr int kXRowBytes = kStageTiles * 128 + 16;   // 8 tiles x 64 halves, padded: conflict-free A loads
 constexpr int kMaxStages = 6;
+constexpr int kTilePitch = 72;                       // padded row of the shared accumulation tile
 
 __host__ __device__ constexpr int stage_bytes(int mt)
 {
@@ -47,7 +49,7 @@ __host__ __device__ constexpr int stage_bytes(int mt)
 struct SkinnySmem {
     uint64_t full[kMaxStages];
     uint64_t empty[kMaxStages];
-    float tile[16][64];  // cross-warp accumulation of one tile row's [rows][64 channels]
+    float tile[16][kTilePitch];  // cross-warp accumulation of one tile row's [tokens][64 channels]
     int flag;
     volatile int abort;
 };
@@ -80,7 +82,7 @@ gemm_skinny_kernel(GemmArgs a, int n_stages)
         sm.abort = 0;
         mbar_fence_init();
     }
-    for (int e = threadIdx.x; e < 16 * 64; e += blockDim.x) (&sm.tile[0][0])[e] = 0.f;
+    for (int e = threadIdx.x; e < 16 * kTilePitch; e += blockDim.x) (&sm.tile[0][0])[e] = 0.f;
     __syncthreads();
 
     if (warp == kConsumerWarps) {
@@ -114,18 +116,25 @@ gemm_skinny_kernel(GemmArgs a, int n_stages)
     }
 
     // ---------------------------------------------------------------------- consumer warps
+    // mma.m16n8k16 with the WEIGHTS as the 16-row A operand (16 channels x 16 reduction indices) and the
+    // activations as the 8-column B operand (8 tokens): a batch of up to 8 tokens costs one MMA per 256
+    // weights.  The legacy mma.sync path of this GPU is slow enough (about 32 cycles per instruction and
+    // SM sub-partition) that the instruction count decides whether the kernel stays HBM-bound.
+    constexpr int NB = MT / 8;                // token groups of 8
     const int gq = lane >> 2, tq = lane & 3;  // mma fragment coordinates
-    float acc[8][4];
+    float acc[4][NB][4];
 #pragma unroll
-    for (int j = 0; j < 8; ++j)
+    for (int j = 0; j < 4; ++j)
 #pragma unroll
-        for (int c = 0; c < 4; ++c) acc[j][c] = 0.f;
+        for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) acc[j][nb][c] = 0.f;
 
     int it = 0;
     int tile_first_kb = -1;  // first k-tile of the current tile row handled by this CTA
     for (int g = g0; g < g1; ++it) {
         const int nt = g / KT, kb = g - nt * KT;
-        const int nb = min(min(kStageTiles, KT - kb), g1 - g);
+        const int nb_tiles = min(min(kStageTiles, KT - kb), g1 - g);
         const int s = it % n_stages;
         if (tile_first_kb < 0) tile_first_kb = kb;
         if (!sm.abort) {
@@ -135,52 +144,59 @@ gemm_skinny_kernel(GemmArgs a, int n_stages)
             }
         }
         const uint8_t* stage = dyn_smem + (size_t)s * stage_bytes(MT);
-        if (warp < nb) {
-            // activations: rows gq and gq+8, 16 consecutive reduction indices starting at 16*tq
+        if (warp < nb_tiles) {
+            // activations (B operand): token gq (+8 per group), 16 consecutive reduction indices from 16*tq
             const uint8_t* xs = stage + kStageWBytes + warp * 128 + tq * 32;
-            uint4 xa0 = make_uint4(0, 0, 0, 0), xa1 = xa0, xb0 = xa0, xb1 = xa0;
-            if (gq < rows) {
-                xa0 = *reinterpret_cast<const uint4*>(xs + gq * kXRowBytes);
-                xa1 = *reinterpret_cast<const uint4*>(xs + gq * kXRowBytes + 16);
+            uint32_t xw[NB][8];
+#pragma unroll
+            for (int nb = 0; nb < NB; ++nb) {
+                uint4 x0 = make_uint4(0, 0, 0, 0), x1 = x0;
+                if (gq + 8 * nb < rows) {
+                    x0 = *reinterpret_cast<const uint4*>(xs + (gq + 8 * nb) * kXRowBytes);
+                    x1 = *reinterpret_cast<const uint4*>(xs + (gq + 8 * nb) * kXRowBytes + 16);
+                }
+                xw[nb][0] = x0.x; xw[nb][1] = x0.y; xw[nb][2] = x0.z; xw[nb][3] = x0.w;
+                xw[nb][4] = x1.x; xw[nb][5] = x1.y; xw[nb][6] = x1.z; xw[nb][7] = x1.w;
             }
-            if (MT == 16 && gq + 8 < rows) {
-                xb0 = *reinterpret_cast<const uint4*>(xs + (gq + 8) * kXRowBytes);
-                xb1 = *reinterpret_cast<const uint4*>(xs + (gq + 8) * kXRowBytes + 16);
-            }
-            const uint32_t xa[8] = {xa0.x, xa0.y, xa0.z, xa0.w, xa1.x, xa1.y, xa1.z, xa1.w};
-            const uint32_t xb[8] = {xb0.x, xb0.y, xb0.z, xb0.w, xb1.x, xb1.y, xb1.z, xb1.w};
             const uint8_t* ws = stage + warp * kTileBytes + lane * 16;
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                // 8 channels (8j + gq) x 64 reduction indices: this lane gets indices 16*tq .. 16*tq+15
-                const uint4 wv = *reinterpret_cast<const uint4*>(ws + j * 512);
-                const uint32_t w4[4] = {wv.x, wv.y, wv.z, wv.w};
+            for (int j = 0; j < 4; ++j) {
+                // channels 16j + gq and 16j + gq + 8, reduction indices 16*tq .. 16*tq + 15 of this tile
+                const uint4 wa = *reinterpret_cast<const uint4*>(ws + j * 1024);
+                const uint4 wb = *reinterpret_cast<const uint4*>(ws + j * 1024 + 512);
+                const uint32_t wa4[4] = {wa.x, wa.y, wa.z, wa.w};
+                const uint32_t wb4[4] = {wb.x, wb.y, wb.z, wb.w};
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
-                    uint32_t b0, b1;
-                    cvt_u8x4_to_f16x4(w4[i], b0, b1);
-                    mma_m16n8k16(acc[j], xa[2 * i], xb[2 * i], xa[2 * i + 1], xb[2 * i + 1], b0, b1);
+                    uint32_t a0, a1, a2, a3;
+                    cvt_u8x4_to_f16x4(wa4[i], a0, a2);
+                    cvt_u8x4_to_f16x4(wb4[i], a1, a3);
+#pragma unroll
+                    for (int nb = 0; nb < NB; ++nb) {
+                        mma_m16n8k16(acc[j][nb], a0, a1, a2, a3, xw[nb][2 * i], xw[nb][2 * i + 1]);
+                    }
                 }
             }
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(&sm.empty[s]);
-        g += nb;
+        g += nb_tiles;
 
-        const bool row_end = (kb + nb == KT);
+        const bool row_end = (kb + nb_tiles == KT);
         if (row_end || g == g1) {
             // ---- flush the tile row: reduce the 8 warps' fragments through shared memory ----
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const int n = j * 8 + tq * 2;
-                atomicAdd(&sm.tile[gq][n], acc[j][0]);
-                atomicAdd(&sm.tile[gq][n + 1], acc[j][1]);
-                if (MT == 16) {
-                    atomicAdd(&sm.tile[gq + 8][n], acc[j][2]);
-                    atomicAdd(&sm.tile[gq + 8][n + 1], acc[j][3]);
-                }
+            for (int j = 0; j < 4; ++j) {
 #pragma unroll
-                for (int c = 0; c < 4; ++c) acc[j][c] = 0.f;
+                for (int nb = 0; nb < NB; ++nb) {
+                    const int m = nb * 8 + tq * 2, n = j * 16 + gq;
+                    atomicAdd(&sm.tile[m][n], acc[j][nb][0]);
+                    atomicAdd(&sm.tile[m + 1][n], acc[j][nb][1]);
+                    atomicAdd(&sm.tile[m][n + 8], acc[j][nb][2]);
+                    atomicAdd(&sm.tile[m + 1][n + 8], acc[j][nb][3]);
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) acc[j][nb][c] = 0.f;
+                }
             }
             consumer_bar();
             const bool whole_row = (tile_first_kb == 0) && row_end;
@@ -196,7 +212,7 @@ gemm_skinny_kernel(GemmArgs a, int n_stages)
                 __threadfence();
                 consumer_bar();
                 if (threadIdx.x == 0) {
-                    const int contributed = kb + nb - tile_first_kb;
+                    const int contributed = kb + nb_tiles - tile_first_kb;
                     const int old = atomicAdd(counter, contributed);
                     sm.flag = (old + contributed == KT);
                 }
@@ -222,7 +238,9 @@ gemm_skinny_kernel(GemmArgs a, int n_stages)
                 }
                 if (!whole_row && threadIdx.x == 0) *counter = 0;
             }
-            for (int e = threadIdx.x; e < 16 * 64; e += kConsumerThreads) (&sm.tile[0][0])[e] = 0.f;
+            // each thread clears exactly the elements it read above (same e -> (m, n) mapping), so no
+            // barrier is needed between the reads and the clearing
+            for (int e = threadIdx.x; e < 16 * 64; e += kConsumerThreads) sm.tile[e >> 6][e & 63] = 0.f;
             consumer_bar();
             tile_first_kb = -1;
         }
