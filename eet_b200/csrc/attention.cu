@@ -98,6 +98,10 @@ decode_mha_kernel(DecodeAttnArgs a)
     __shared__ __align__(16) float c_acc[D];
     __shared__ float c_ml[2];
 
+    // everything this kernel reads that an earlier kernel of the same step produced (the projection of the
+    // new token, the device-resident step) comes after this wait
+    pdl_launch_dependents();
+    pdl_wait();
     const int step = a.step_dev ? *a.step_dev : a.step;
     const size_t inner = (size_t)a.H * D;
     const __half* qkv = a.qkv + (size_t)b * 3 * inner + (size_t)h * D;
@@ -377,13 +381,15 @@ int launch_decode_mha(const DecodeAttnArgs& a, cudaStream_t stream)
     cfg.blockDim = dim3(kAttnThreads, 1, 1);
     cfg.dynamicSmemBytes = 0;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = splits;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = 2;
     EET_CUDA(cudaLaunchKernelEx(&cfg, decode_mha_kernel, a));
     return 0;
 }

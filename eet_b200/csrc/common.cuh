@@ -151,6 +151,21 @@ __device__ __forceinline__ void mma_m16n8k16(float (&d)[4], uint32_t a0, uint32_
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// Programmatic dependent launch (PDL).  A kernel launched with launch_pdl() may begin while the kernel
+// before it in the stream is still running; pdl_wait() blocks until that kernel has completed and its
+// writes are visible, so everything that reads or writes data of the dependency chain comes after it.
+// pdl_launch_dependents() tells the scheduler that the next kernel may be started.  Both are no-ops for
+// a kernel launched without the attribute.
+__device__ __forceinline__ void pdl_wait()
+{
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+__device__ __forceinline__ void pdl_launch_dependents()
+{
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 __device__ __forceinline__ float warp_sum(float v)
 {
 #pragma unroll
@@ -167,6 +182,24 @@ __device__ __forceinline__ float warp_max(float v)
         v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
     }
     return v;
+}
+
+// Launches `kernel` with the programmatic-stream-serialization attribute (see pdl_wait above).
+template<typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              Args... args)
+{
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }
 
 #endif  // __CUDACC__

@@ -7,20 +7,23 @@
 // :80-84), far too few bytes in flight for HBM.
 //
 // B200 design.  The job is HBM-bound: N*K weight bytes are read once.
-//  * Stream-K partition: the W8T64 tiles are numbered [N/64][K/64] in memory order; the grid is one
-//    persistent CTA per SM and CTA c owns an equal, contiguous run of tiles, i.e. one linear byte range
+//  * Stream-K partition: the W8T64 tiles are numbered [N/64][K/64] in memory order; the grid is two
+//    persistent CTAs per SM and CTA c owns an equal, contiguous run of tiles, i.e. one linear byte range
 //    of the weight array, whatever N and K are.
-//  * A producer warp feeds a ring of shared-memory stages with 1-D bulk copies (TMA engine,
-//    cp.async.bulk + mbarrier complete_tx): up to 32 KiB of weights plus the matching slice of the
-//    activations per stage, 4-5 stages in flight per SM.
+//  * A producer warp feeds a ring of three 32 KiB shared-memory stages with 1-D bulk copies (TMA engine,
+//    cp.async.bulk + mbarrier complete_tx, L2 evict-first).  Two CTAs per SM keep six stages in flight.
 //  * Eight consumer warps each take one 64x64 tile of a stage: 16-byte shared loads deliver exactly the
 //    A fragments of mma.m16n8k16 (16 channels x 64 reduction indices per pair of loads), bytes become
-//    fp16 in registers (prmt + sub.f16x2) and feed the tensor cores with up to 8 tokens as the B operand;
-//    the reduction index is permuted identically on both operands, so no shuffles or transposes are
-//    needed.
+//    fp16 in registers (prmt + sub.f16x2) and feed the tensor cores with up to 8 tokens as the B operand,
+//    which comes straight from global memory (L1/L2 resident, prefetched one tile ahead); the reduction
+//    index is permuted identically on both operands, so no shuffles or transposes are needed.
 //  * When a CTA's run ends inside a tile row, partial sums go to an fp32 scratch with red.global.add and
 //    a per-tile-row arrival counter; the CTA that completes the count applies the scale (and residual),
 //    writes fp16, and restores the scratch to zero.  Tile rows covered by one CTA skip the scratch.
+//  * Programmatic dependent launch: the kernel may start while its predecessor in the stream is still
+//    draining.  Weights do not depend on earlier kernels, so the producer streams them at once; only the
+//    consumers wait (griddepcontrol.wait) before they touch activations, scratch or the output.  Back to
+//    back GEMMs of a decode step therefore keep HBM busy across kernel boundaries.
 //
 // Numerics: products of fp16 activations with exact integer weights, fp32 accumulation, one multiply by
 // the fp16 scale, one rounding to fp16 (the reference rounds every q*scale to fp16 first and rounds the
@@ -35,20 +38,15 @@ namespace {
 constexpr int kConsumerWarps = 8;
 constexpr int kConsumerThreads = kConsumerWarps * 32;
 constexpr int kSkinnyThreads = kConsumerThreads + 32;
-constexpr int kStageTiles = 8;                       // W8T64 tiles per stage
-constexpr int kStageWBytes = kStageTiles * kTileBytes;
-constexpr int kXRowBytes = kStageTiles * 128 + 16;   // 8 tiles x 64 halves, padded: conflict-free A loads
-constexpr int kMaxStages = 6;
-constexpr int kTilePitch = 72;                       // padded row of the shared accumulation tile
-
-__host__ __device__ constexpr int stage_bytes(int mt)
-{
-    return kStageWBytes + mt * kXRowBytes;
-}
+constexpr int kStageTiles = 8;  // W8T64 tiles per stage
+constexpr int kStageBytes = kStageTiles * kTileBytes;
+constexpr int kStages = 3;
+constexpr int kTilePitch = 72;  // padded row of the shared accumulation tile
+constexpr int kSkinnyCtasPerSm = 2;
 
 struct SkinnySmem {
-    uint64_t full[kMaxStages];
-    uint64_t empty[kMaxStages];
+    uint64_t full[kStages];
+    uint64_t empty[kStages];
     float tile[16][kTilePitch];  // cross-warp accumulation of one tile row's [tokens][64 channels]
     int flag;
     volatile int abort;
@@ -59,23 +57,42 @@ __device__ __forceinline__ void consumer_bar()
     asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
 }
 
-template<int MT>
-__global__ void __launch_bounds__(kSkinnyThreads, 1)
-gemm_skinny_kernel(GemmArgs a, int n_stages)
+// Activation fragment of one 64-wide reduction tile for this lane: token `row`, 16 consecutive reduction
+// indices starting at 16 * tq (two 16-byte loads; L1/L2 hits after the first touch).
+__device__ __forceinline__ void load_x(uint32_t (&xw)[8], const __half* A, int K, int row, int rows, int m0, int kb,
+                                       int tq)
+{
+    uint4 x0 = make_uint4(0, 0, 0, 0), x1 = x0;
+    if (row < rows) {
+        const uint4* p = reinterpret_cast<const uint4*>(A + (size_t)(m0 + row) * K + (size_t)kb * kTile + tq * 16);
+        x0 = __ldg(p);
+        x1 = __ldg(p + 1);
+    }
+    xw[0] = x0.x; xw[1] = x0.y; xw[2] = x0.z; xw[3] = x0.w;
+    xw[4] = x1.x; xw[5] = x1.y; xw[6] = x1.z; xw[7] = x1.w;
+}
+
+// NB = token groups of 8 handled per pass (1: M <= 8, 2: M <= 16).
+template<int NB>
+__global__ void __launch_bounds__(kSkinnyThreads, kSkinnyCtasPerSm)
+gemm_skinny_kernel(GemmArgs a)
 {
     extern __shared__ __align__(128) uint8_t dyn_smem[];
     __shared__ SkinnySmem sm;
+
+    // let the next kernel in the stream start its own weight streaming as soon as SM resources allow
+    pdl_launch_dependents();
 
     const int KT = a.K / kTile, NT = a.N / kTile;
     const long long G = (long long)NT * KT;
     const int g0 = (int)(G * blockIdx.x / gridDim.x);
     const int g1 = (int)(G * (blockIdx.x + 1) / gridDim.x);
     const int m0 = blockIdx.y * 16;
-    const int rows = min(MT, a.M - m0);
+    const int rows = min(8 * NB, a.M - m0);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < n_stages; ++s) {
+        for (int s = 0; s < kStages; ++s) {
             mbar_init(&sm.full[s], 1);
             mbar_init(&sm.empty[s], kConsumerWarps);
         }
@@ -86,31 +103,25 @@ gemm_skinny_kernel(GemmArgs a, int n_stages)
     __syncthreads();
 
     if (warp == kConsumerWarps) {
-        // ------------------------------------------------------------------ producer warp
-        int it = 0;
-        for (int g = g0; g < g1; ++it) {
-            const int nt = g / KT, kb = g - nt * KT;
-            const int nb = min(min(kStageTiles, KT - kb), g1 - g);
-            const int s = it % n_stages;
-            if (it >= n_stages && !sm.abort) {
-                if (!mbar_wait_bounded(&sm.empty[s], ((it / n_stages) - 1) & 1)) {
-                    sm.abort = 1;
-                    g_device_status = 1;
+        // ------------------------------------------------------------------ producer warp (one lane)
+        // Weights are constant inputs: no need to wait for the preceding kernel.
+        if (lane == 0) {
+            int it = 0;
+            for (int g = g0; g < g1; ++it) {
+                const int nt = g / KT, kb = g - nt * KT;
+                const int nb_tiles = min(min(kStageTiles, KT - kb), g1 - g);
+                const int s = it % kStages;
+                if (it >= kStages && !sm.abort) {
+                    if (!mbar_wait_bounded(&sm.empty[s], ((it / kStages) - 1) & 1)) {
+                        sm.abort = 1;
+                        g_device_status = 1;
+                    }
                 }
+                mbar_arrive_expect_tx(&sm.full[s], (uint32_t)(nb_tiles * kTileBytes));
+                bulk_g2s_stream(dyn_smem + (size_t)s * kStageBytes, a.B + (size_t)g * kTileBytes,
+                                (uint32_t)(nb_tiles * kTileBytes), &sm.full[s]);
+                g += nb_tiles;
             }
-            uint8_t* stage = dyn_smem + (size_t)s * stage_bytes(MT);
-            if (lane == 0) {
-                mbar_arrive_expect_tx(&sm.full[s], (uint32_t)(nb * kTileBytes + rows * nb * 128));
-            }
-            __syncwarp();
-            if (lane == 0) {
-                bulk_g2s_stream(stage, a.B + (size_t)g * kTileBytes, (uint32_t)(nb * kTileBytes), &sm.full[s]);
-            }
-            if (lane < rows) {
-                bulk_g2s(stage + kStageWBytes + lane * kXRowBytes, a.A + (size_t)(m0 + lane) * a.K + (size_t)kb * kTile,
-                         (uint32_t)(nb * 128), &sm.full[s]);
-            }
-            g += nb;
         }
         return;
     }
@@ -120,7 +131,6 @@ gemm_skinny_kernel(GemmArgs a, int n_stages)
     // activations as the 8-column B operand (8 tokens): a batch of up to 8 tokens costs one MMA per 256
     // weights.  The legacy mma.sync path of this GPU is slow enough (about 32 cycles per instruction and
     // SM sub-partition) that the instruction count decides whether the kernel stays HBM-bound.
-    constexpr int NB = MT / 8;                // token groups of 8
     const int gq = lane >> 2, tq = lane & 3;  // mma fragment coordinates
     float acc[4][NB][4];
 #pragma unroll
@@ -130,35 +140,49 @@ gemm_skinny_kernel(GemmArgs a, int n_stages)
 #pragma unroll
             for (int c = 0; c < 4; ++c) acc[j][nb][c] = 0.f;
 
+    // activations, scratch and output belong to the dependency chain: wait for the preceding kernel
+    pdl_wait();
+
+    // schedule walk shared with the producer: stage `it` holds tiles [g, g + nb_tiles) of one tile row
     int it = 0;
     int tile_first_kb = -1;  // first k-tile of the current tile row handled by this CTA
+    uint32_t xw[NB][8], xn[NB][8];
+    {
+        // prefetch the activations of this warp's tile in the first stage
+        const int nt = g0 / KT, kb = g0 - nt * KT;
+        const int nb_tiles = (g0 < g1) ? min(min(kStageTiles, KT - kb), g1 - g0) : 0;
+#pragma unroll
+        for (int nb = 0; nb < NB; ++nb) {
+            load_x(xn[nb], a.A, a.K, (warp < nb_tiles) ? gq + 8 * nb : rows, rows, m0, kb + warp, tq);
+        }
+    }
     for (int g = g0; g < g1; ++it) {
         const int nt = g / KT, kb = g - nt * KT;
         const int nb_tiles = min(min(kStageTiles, KT - kb), g1 - g);
-        const int s = it % n_stages;
+        const int s = it % kStages;
         if (tile_first_kb < 0) tile_first_kb = kb;
+#pragma unroll
+        for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+            for (int w = 0; w < 8; ++w) xw[nb][w] = xn[nb][w];
+        {
+            // prefetch the next stage's activations before blocking on this stage's weights
+            const int gn = g + nb_tiles;
+            const int ntn = gn / KT, kbn = gn - ntn * KT;
+            const int nbn = (gn < g1) ? min(min(kStageTiles, KT - kbn), g1 - gn) : 0;
+#pragma unroll
+            for (int nb = 0; nb < NB; ++nb) {
+                load_x(xn[nb], a.A, a.K, (warp < nbn) ? gq + 8 * nb : rows, rows, m0, kbn + warp, tq);
+            }
+        }
         if (!sm.abort) {
-            if (!mbar_wait_bounded(&sm.full[s], (it / n_stages) & 1)) {
+            if (!mbar_wait_bounded(&sm.full[s], (it / kStages) & 1)) {
                 sm.abort = 1;
                 g_device_status = 1;
             }
         }
-        const uint8_t* stage = dyn_smem + (size_t)s * stage_bytes(MT);
         if (warp < nb_tiles) {
-            // activations (B operand): token gq (+8 per group), 16 consecutive reduction indices from 16*tq
-            const uint8_t* xs = stage + kStageWBytes + warp * 128 + tq * 32;
-            uint32_t xw[NB][8];
-#pragma unroll
-            for (int nb = 0; nb < NB; ++nb) {
-                uint4 x0 = make_uint4(0, 0, 0, 0), x1 = x0;
-                if (gq + 8 * nb < rows) {
-                    x0 = *reinterpret_cast<const uint4*>(xs + (gq + 8 * nb) * kXRowBytes);
-                    x1 = *reinterpret_cast<const uint4*>(xs + (gq + 8 * nb) * kXRowBytes + 16);
-                }
-                xw[nb][0] = x0.x; xw[nb][1] = x0.y; xw[nb][2] = x0.z; xw[nb][3] = x0.w;
-                xw[nb][4] = x1.x; xw[nb][5] = x1.y; xw[nb][6] = x1.z; xw[nb][7] = x1.w;
-            }
-            const uint8_t* ws = stage + warp * kTileBytes + lane * 16;
+            const uint8_t* ws = dyn_smem + (size_t)s * kStageBytes + warp * kTileBytes + lane * 16;
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 // channels 16j + gq and 16j + gq + 8, reduction indices 16*tq .. 16*tq + 15 of this tile
@@ -266,9 +290,10 @@ int launch_gemm_skinny(const GemmArgs& a, cudaStream_t stream)
     EET_CUDA(cudaGetDevice(&dev));
     dev &= 63;
     const long long G = (long long)(a.N / kTile) * (a.K / kTile);
-    int grid_x = sm_count();
+    int grid_x = kSkinnyCtasPerSm * sm_count();
     if (grid_x > G) grid_x = (int)G;
     const int total_chunks = (a.M + 15) / 16;
+    const size_t smem = (size_t)kStages * kStageBytes;
     for (int c0 = 0; c0 < total_chunks; c0 += 8) {
         const int chunks = (total_chunks - c0 < 8) ? (total_chunks - c0) : 8;
         GemmArgs b = a;
@@ -277,17 +302,13 @@ int launch_gemm_skinny(const GemmArgs& a, cudaStream_t stream)
         if (a.residual) b.residual = a.residual + (size_t)c0 * 16 * a.N;
         b.M = a.M - c0 * 16;
         if (b.M > chunks * 16) b.M = chunks * 16;
-        const bool mt8 = (b.M <= 8);
-        const int mt = mt8 ? 8 : 16;
-        const int stages = mt8 ? 5 : 4;
-        const size_t smem = (size_t)stages * stage_bytes(mt);
-        auto kern = mt8 ? gemm_skinny_kernel<8> : gemm_skinny_kernel<16>;
-        if (!attr_set[dev][mt8 ? 0 : 1]) {
+        const bool one_group = (b.M <= 8);
+        auto kern = one_group ? gemm_skinny_kernel<1> : gemm_skinny_kernel<2>;
+        if (!attr_set[dev][one_group ? 0 : 1]) {
             EET_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            attr_set[dev][mt8 ? 0 : 1] = true;
+            attr_set[dev][one_group ? 0 : 1] = true;
         }
-        kern<<<dim3(grid_x, chunks), kSkinnyThreads, smem, stream>>>(b, stages);
-        EET_LAUNCH_CHECK();
+        EET_CUDA(launch_pdl(kern, dim3(grid_x, chunks), dim3(kSkinnyThreads), smem, stream, b));
     }
     return 0;
 }

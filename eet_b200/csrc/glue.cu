@@ -19,6 +19,8 @@ rmsnorm_kernel(const __half* __restrict__ x, const __half* __restrict__ gamma, _
 {
     __shared__ float red[32];
     __shared__ float s_inv;
+    pdl_launch_dependents();
+    pdl_wait();
     const int row = blockIdx.x;
     const int nv = n >> 3;
     const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)row * n);
@@ -82,6 +84,8 @@ __device__ __forceinline__ __half2 gated_silu2(__half2 g, __half2 u)
 __global__ void __launch_bounds__(256)
 swiglu_kernel(__half* __restrict__ gate, const __half* __restrict__ up, size_t nvec)
 {
+    pdl_launch_dependents();
+    pdl_wait();
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= nvec) return;
     uint4 g = reinterpret_cast<uint4*>(gate)[i];
@@ -97,6 +101,8 @@ swiglu_kernel(__half* __restrict__ gate, const __half* __restrict__ up, size_t n
 __global__ void __launch_bounds__(256)
 add_residual_kernel(__half* __restrict__ out, const __half* __restrict__ in, size_t nvec)
 {
+    pdl_launch_dependents();
+    pdl_wait();
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= nvec) return;
     uint4 o = reinterpret_cast<uint4*>(out)[i];
@@ -187,6 +193,8 @@ scatter_kv_kernel(__half* __restrict__ kcache, __half* __restrict__ vcache, int 
 
 __global__ void advance_steps_kernel(int* steps, int count, int delta)
 {
+    pdl_launch_dependents();
+    pdl_wait();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < count) steps[i] += delta;
 }
@@ -201,8 +209,7 @@ int launch_rmsnorm(const __half* x, const __half* gamma, __half* y, int M, int n
     int threads = ((nv + 1) / 2 + 31) / 32 * 32;
     if (threads < 32) threads = 32;
     if (threads > 1024) threads = 1024;
-    rmsnorm_kernel<<<M, threads, 0, stream>>>(x, gamma, y, n, eps);
-    EET_LAUNCH_CHECK();
+    EET_CUDA(launch_pdl(rmsnorm_kernel, dim3(M), dim3(threads), 0, stream, x, gamma, y, n, eps));
     return 0;
 }
 
@@ -211,8 +218,7 @@ int launch_swiglu(__half* gate_inout, const __half* up, int M, int n, cudaStream
     EET_CHECK(n % 8 == 0, "swiglu: inner size %d must be a multiple of 8", n);
     const size_t nvec = (size_t)M * n / 8;
     if (nvec == 0) return 0;
-    swiglu_kernel<<<(unsigned)((nvec + 255) / 256), 256, 0, stream>>>(gate_inout, up, nvec);
-    EET_LAUNCH_CHECK();
+    EET_CUDA(launch_pdl(swiglu_kernel, dim3((unsigned)((nvec + 255) / 256)), dim3(256), 0, stream, gate_inout, up, nvec));
     return 0;
 }
 
@@ -221,8 +227,7 @@ int launch_add_residual(__half* out, const __half* in, size_t count, cudaStream_
     EET_CHECK(count % 8 == 0, "add_residual: element count must be a multiple of 8");
     const size_t nvec = count / 8;
     if (nvec == 0) return 0;
-    add_residual_kernel<<<(unsigned)((nvec + 255) / 256), 256, 0, stream>>>(out, in, nvec);
-    EET_LAUNCH_CHECK();
+    EET_CUDA(launch_pdl(add_residual_kernel, dim3((unsigned)((nvec + 255) / 256)), dim3(256), 0, stream, out, in, nvec));
     return 0;
 }
 
@@ -258,8 +263,7 @@ int launch_reorder_kv(__half* kcache, __half* vcache, const int64_t* index, int 
 int launch_advance_steps(int* steps, int count, int delta, cudaStream_t stream)
 {
     if (count <= 0) return 0;
-    advance_steps_kernel<<<(count + 127) / 128, 128, 0, stream>>>(steps, count, delta);
-    EET_LAUNCH_CHECK();
+    EET_CUDA(launch_pdl(advance_steps_kernel, dim3((count + 127) / 128), dim3(128), 0, stream, steps, count, delta));
     return 0;
 }
 
