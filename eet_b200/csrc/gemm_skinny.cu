@@ -10,16 +10,19 @@
 //  * Stream-K partition: the W8T64 tiles are numbered [N/64][K/64] in memory order; the grid is two
 //    persistent CTAs per SM and CTA c owns an equal, contiguous run of tiles, i.e. one linear byte range
 //    of the weight array, whatever N and K are.
-//  * A producer warp feeds a ring of three 32 KiB shared-memory stages with 1-D bulk copies (TMA engine,
-//    cp.async.bulk + mbarrier complete_tx, L2 evict-first).  Two CTAs per SM keep six stages in flight.
-//  * Eight consumer warps each take one 64x64 tile of a stage: 16-byte shared loads deliver exactly the
-//    A fragments of mma.m16n8k16 (16 channels x 64 reduction indices per pair of loads), bytes become
-//    fp16 in registers (prmt + sub.f16x2) and feed the tensor cores with up to 8 tokens as the B operand,
-//    which comes straight from global memory (L1/L2 resident, prefetched one tile ahead); the reduction
-//    index is permuted identically on both operands, so no shuffles or transposes are needed.
+//  * A producer warp feeds a ring of shared-memory stages with 1-D bulk copies (TMA engine,
+//    cp.async.bulk + mbarrier complete_tx, L2 evict-first hint): 24 KiB of weights (six tiles) per stage,
+//    three stages per CTA, two CTAs per SM.  The matching slice of the activations (a few KiB, L2
+//    resident) is staged beside it by the consumer warps with plain 16-byte loads, one stage ahead.
+//  * Eight consumer warps share a stage by channel group and tile half: 16-byte shared loads deliver
+//    exactly the A fragments of mma.m16n8k16 (16 channels x 64 reduction indices per pair of loads),
+//    bytes become fp16 in registers (prmt + sub.f16x2) and feed the tensor cores with up to 8 tokens as
+//    the B operand; the reduction index is permuted identically on both operands, so no shuffles or
+//    transposes are needed, and a warp's accumulators stay in registers for a whole tile row.
 //  * When a CTA's run ends inside a tile row, partial sums go to an fp32 scratch with red.global.add and
-//    a per-tile-row arrival counter; the CTA that completes the count applies the scale (and residual),
-//    writes fp16, and restores the scratch to zero.  Tile rows covered by one CTA skip the scratch.
+//    an arrival counter per 16 channels; the warp that completes the count applies the scale (and
+//    residual), writes fp16, and restores the scratch to zero.  Tile rows covered by one CTA skip the
+//    scratch.
 //  * Programmatic dependent launch: the kernel may start while its predecessor in the stream is still
 //    draining.  Weights do not depend on earlier kernels, so the producer streams them at once; only the
 //    consumers wait (griddepcontrol.wait) before they touch activations, scratch or the output.  Back to
@@ -38,38 +41,31 @@ namespace {
 constexpr int kConsumerWarps = 8;
 constexpr int kConsumerThreads = kConsumerWarps * 32;
 constexpr int kSkinnyThreads = kConsumerThreads + 32;
-constexpr int kStageTiles = 8;  // W8T64 tiles per stage
-constexpr int kStageBytes = kStageTiles * kTileBytes;
-constexpr int kStages = 3;
-constexpr int kTilePitch = 72;  // padded row of the shared accumulation tile
+constexpr int kStageTiles = 6;  // W8T64 tiles per stage: three for each half of the consumer warps
+constexpr int kStageWBytes = kStageTiles * kTileBytes;
+constexpr int kXRowBytes = kStageTiles * 128 + 16;  // one token's slice of a stage, padded: conflict-free loads
+constexpr int kMaxStages = 3;
 constexpr int kSkinnyCtasPerSm = 2;
 
+__host__ __device__ constexpr int stage_bytes(int nb)
+{
+    return kStageWBytes + 8 * nb * kXRowBytes;
+}
+__host__ __device__ constexpr int stage_count(int nb)
+{
+    return nb == 1 ? 3 : 2;  // 3 x 30.1 KiB or 2 x 36.3 KiB: two CTAs fit in one SM's shared memory
+}
+
 struct SkinnySmem {
-    uint64_t full[kStages];
-    uint64_t empty[kStages];
-    float tile[16][kTilePitch];  // cross-warp accumulation of one tile row's [tokens][64 channels]
-    int flag;
+    uint64_t full[kMaxStages];
+    uint64_t empty[kMaxStages];
+    float fold[4][2][32][4];  // fragments of warps 4-7 on their way to warps 0-3 at the end of a tile row
     volatile int abort;
 };
 
 __device__ __forceinline__ void consumer_bar()
 {
     asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
-}
-
-// Activation fragment of one 64-wide reduction tile for this lane: token `row`, 16 consecutive reduction
-// indices starting at 16 * tq (two 16-byte loads; L1/L2 hits after the first touch).
-__device__ __forceinline__ void load_x(uint32_t (&xw)[8], const __half* A, int K, int row, int rows, int m0, int kb,
-                                       int tq)
-{
-    uint4 x0 = make_uint4(0, 0, 0, 0), x1 = x0;
-    if (row < rows) {
-        const uint4* p = reinterpret_cast<const uint4*>(A + (size_t)(m0 + row) * K + (size_t)kb * kTile + tq * 16);
-        x0 = __ldg(p);
-        x1 = __ldg(p + 1);
-    }
-    xw[0] = x0.x; xw[1] = x0.y; xw[2] = x0.z; xw[3] = x0.w;
-    xw[4] = x1.x; xw[5] = x1.y; xw[6] = x1.z; xw[7] = x1.w;
 }
 
 // NB = token groups of 8 handled per pass (1: M <= 8, 2: M <= 16).
@@ -90,6 +86,8 @@ gemm_skinny_kernel(GemmArgs a)
     const int m0 = blockIdx.y * 16;
     const int rows = min(8 * NB, a.M - m0);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    constexpr int kStages = stage_count(NB);
+    constexpr int kStageBytes = stage_bytes(NB);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
@@ -99,7 +97,6 @@ gemm_skinny_kernel(GemmArgs a)
         sm.abort = 0;
         mbar_fence_init();
     }
-    for (int e = threadIdx.x; e < 16 * kTilePitch; e += blockDim.x) (&sm.tile[0][0])[e] = 0.f;
     __syncthreads();
 
     if (warp == kConsumerWarps) {
@@ -131,48 +128,77 @@ gemm_skinny_kernel(GemmArgs a)
     // activations as the 8-column B operand (8 tokens): a batch of up to 8 tokens costs one MMA per 256
     // weights.  The legacy mma.sync path of this GPU is slow enough (about 32 cycles per instruction and
     // SM sub-partition) that the instruction count decides whether the kernel stays HBM-bound.
+    //
+    // Warp w owns channel group cg = w % 4 (channels 16cg .. 16cg+15 of the tile row) and half kh = w / 4
+    // of the tiles of each stage, so its accumulators never leave registers until the tile row ends; then
+    // the two halves meet through 4 KiB of shared memory and warps 0-3 run the epilogue from registers.
     const int gq = lane >> 2, tq = lane & 3;  // mma fragment coordinates
-    float acc[4][NB][4];
+    const int cg = warp & 3, kh = warp >> 2;
+    float acc[NB][4];
 #pragma unroll
-    for (int j = 0; j < 4; ++j)
+    for (int nb = 0; nb < NB; ++nb)
 #pragma unroll
-        for (int nb = 0; nb < NB; ++nb)
-#pragma unroll
-            for (int c = 0; c < 4; ++c) acc[j][nb][c] = 0.f;
+        for (int c = 0; c < 4; ++c) acc[nb][c] = 0.f;
 
     // activations, scratch and output belong to the dependency chain: wait for the preceding kernel
     pdl_wait();
 
+    // The four warps of a half stage the activations of their three tiles themselves: 16-byte global loads
+    // (L2 hits) one stage ahead into registers, then into the stage's padded slab.
+    constexpr int kHalfTiles = kStageTiles / 2;
+    constexpr int kXChunks = 8 * NB * kHalfTiles * 8;          // 16-byte chunks per half and stage
+    constexpr int kXPerThread = (kXChunks + 127) / 128;
+    const int hl = threadIdx.x & 127;
+    uint4 xr[kXPerThread];
+    auto fetch_x = [&](int kb_stage, int nb_tiles_stage) {
+#pragma unroll
+        for (int u = 0; u < kXPerThread; ++u) {
+            const int c = hl + u * 128;
+            const int row = c / (kHalfTiles * 8), col = c % (kHalfTiles * 8);
+            const int tile = kh * kHalfTiles + (col >> 3);
+            xr[u] = make_uint4(0, 0, 0, 0);
+            if (c < kXChunks && row < rows && tile < nb_tiles_stage) {
+                xr[u] = __ldg(reinterpret_cast<const uint4*>(a.A + (size_t)(m0 + row) * a.K +
+                                                             (size_t)(kb_stage + kh * kHalfTiles) * kTile) + col);
+            }
+        }
+    };
+
     // schedule walk shared with the producer: stage `it` holds tiles [g, g + nb_tiles) of one tile row
     int it = 0;
     int tile_first_kb = -1;  // first k-tile of the current tile row handled by this CTA
-    uint32_t xw[NB][8], xn[NB][8];
-    {
-        // prefetch the activations of this warp's tile in the first stage
+    if (g0 < g1) {
         const int nt = g0 / KT, kb = g0 - nt * KT;
-        const int nb_tiles = (g0 < g1) ? min(min(kStageTiles, KT - kb), g1 - g0) : 0;
-#pragma unroll
-        for (int nb = 0; nb < NB; ++nb) {
-            load_x(xn[nb], a.A, a.K, (warp < nb_tiles) ? gq + 8 * nb : rows, rows, m0, kb + warp, tq);
-        }
+        fetch_x(kb, min(min(kStageTiles, KT - kb), g1 - g0));
     }
     for (int g = g0; g < g1; ++it) {
         const int nt = g / KT, kb = g - nt * KT;
         const int nb_tiles = min(min(kStageTiles, KT - kb), g1 - g);
         const int s = it % kStages;
         if (tile_first_kb < 0) tile_first_kb = kb;
-#pragma unroll
-        for (int nb = 0; nb < NB; ++nb)
-#pragma unroll
-            for (int w = 0; w < 8; ++w) xw[nb][w] = xn[nb][w];
         {
-            // prefetch the next stage's activations before blocking on this stage's weights
-            const int gn = g + nb_tiles;
-            const int ntn = gn / KT, kbn = gn - ntn * KT;
-            const int nbn = (gn < g1) ? min(min(kStageTiles, KT - kbn), g1 - gn) : 0;
+            uint8_t* xdst = dyn_smem + (size_t)s * kStageBytes + kStageWBytes + kh * kHalfTiles * 128;
 #pragma unroll
-            for (int nb = 0; nb < NB; ++nb) {
-                load_x(xn[nb], a.A, a.K, (warp < nbn) ? gq + 8 * nb : rows, rows, m0, kbn + warp, tq);
+            for (int u = 0; u < kXPerThread; ++u) {
+                const int c = hl + u * 128;
+                if (c < kXChunks) {
+                    const int row = c / (kHalfTiles * 8), col = c % (kHalfTiles * 8);
+                    *reinterpret_cast<uint4*>(xdst + row * kXRowBytes + col * 16) = xr[u];
+                }
+            }
+            // next stage's activations: in flight while this stage is computed
+            const int gn = g + nb_tiles;
+            if (gn < g1) {
+                const int ntn = gn / KT, kbn = gn - ntn * KT;
+                fetch_x(kbn, min(min(kStageTiles, KT - kbn), g1 - gn));
+            }
+            // slab complete for the four warps of this half (a warp can be at most one stage ahead of the
+            // others, and the ring has at least two stages, so the slab being refilled is no longer read)
+            if (kh == 0) {
+                asm volatile("bar.sync 2, 128;" ::: "memory");
+            }
+            else {
+                asm volatile("bar.sync 3, 128;" ::: "memory");
             }
         }
         if (!sm.abort) {
@@ -181,13 +207,27 @@ gemm_skinny_kernel(GemmArgs a)
                 g_device_status = 1;
             }
         }
-        if (warp < nb_tiles) {
-            const uint8_t* ws = dyn_smem + (size_t)s * kStageBytes + warp * kTileBytes + lane * 16;
+        // channels 16cg + gq and 16cg + gq + 8, reduction indices 16*tq .. 16*tq + 15 of each tile
+        const uint8_t* stage = dyn_smem + (size_t)s * kStageBytes;
+        const uint8_t* ws = stage + cg * 1024 + lane * 16;
+        const uint8_t* xs = stage + kStageWBytes + tq * 32;
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                // channels 16j + gq and 16j + gq + 8, reduction indices 16*tq .. 16*tq + 15 of this tile
-                const uint4 wa = *reinterpret_cast<const uint4*>(ws + j * 1024);
-                const uint4 wb = *reinterpret_cast<const uint4*>(ws + j * 1024 + 512);
+        for (int t = 0; t < kStageTiles / 2; ++t) {
+            const int tile = kh * (kStageTiles / 2) + t;
+            if (tile < nb_tiles) {
+                // activations (B operand): token gq (+8 per group), the same 16 reduction indices
+                uint32_t xw[NB][8];
+#pragma unroll
+                for (int nb = 0; nb < NB; ++nb) {
+                    // (rows beyond the batch were stored as zeros)
+                    const uint8_t* xp = xs + (gq + 8 * nb) * kXRowBytes + tile * 128;
+                    const uint4 x0 = *reinterpret_cast<const uint4*>(xp);
+                    const uint4 x1 = *reinterpret_cast<const uint4*>(xp + 16);
+                    xw[nb][0] = x0.x; xw[nb][1] = x0.y; xw[nb][2] = x0.z; xw[nb][3] = x0.w;
+                    xw[nb][4] = x1.x; xw[nb][5] = x1.y; xw[nb][6] = x1.z; xw[nb][7] = x1.w;
+                }
+                const uint4 wa = *reinterpret_cast<const uint4*>(ws + tile * kTileBytes);
+                const uint4 wb = *reinterpret_cast<const uint4*>(ws + tile * kTileBytes + 512);
                 const uint32_t wa4[4] = {wa.x, wa.y, wa.z, wa.w};
                 const uint32_t wb4[4] = {wb.x, wb.y, wb.z, wb.w};
 #pragma unroll
@@ -197,7 +237,7 @@ gemm_skinny_kernel(GemmArgs a)
                     cvt_u8x4_to_f16x4(wb4[i], a1, a3);
 #pragma unroll
                     for (int nb = 0; nb < NB; ++nb) {
-                        mma_m16n8k16(acc[j][nb], a0, a1, a2, a3, xw[nb][2 * i], xw[nb][2 * i + 1]);
+                        mma_m16n8k16(acc[nb], a0, a1, a2, a3, xw[nb][2 * i], xw[nb][2 * i + 1]);
                     }
                 }
             }
@@ -208,64 +248,103 @@ gemm_skinny_kernel(GemmArgs a)
 
         const bool row_end = (kb + nb_tiles == KT);
         if (row_end || g == g1) {
-            // ---- flush the tile row: reduce the 8 warps' fragments through shared memory ----
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
+            // ---- end of this CTA's share of the tile row: fold the two k-halves, then the epilogue ----
+            if (kh == 1) {
 #pragma unroll
                 for (int nb = 0; nb < NB; ++nb) {
-                    const int m = nb * 8 + tq * 2, n = j * 16 + gq;
-                    atomicAdd(&sm.tile[m][n], acc[j][nb][0]);
-                    atomicAdd(&sm.tile[m + 1][n], acc[j][nb][1]);
-                    atomicAdd(&sm.tile[m][n + 8], acc[j][nb][2]);
-                    atomicAdd(&sm.tile[m + 1][n + 8], acc[j][nb][3]);
+                    *reinterpret_cast<float4*>(&sm.fold[cg][nb][lane][0]) =
+                        make_float4(acc[nb][0], acc[nb][1], acc[nb][2], acc[nb][3]);
 #pragma unroll
-                    for (int c = 0; c < 4; ++c) acc[j][nb][c] = 0.f;
+                    for (int c = 0; c < 4; ++c) acc[nb][c] = 0.f;
                 }
             }
             consumer_bar();
-            const bool whole_row = (tile_first_kb == 0) && row_end;
-            const int n_base = nt * kTile;
-            float* ws_tile = a.ws + (size_t)m0 * a.N + n_base;
-            int* counter = reinterpret_cast<int*>(a.ws + (size_t)gridDim.y * 16 * a.N) + blockIdx.y * NT + nt;
-            bool finalize = whole_row;
-            if (!whole_row) {
-                for (int e = threadIdx.x; e < rows * 64; e += kConsumerThreads) {
-                    const int m = e >> 6, n = e & 63;
-                    atomicAdd(ws_tile + (size_t)m * a.N + n, sm.tile[m][n]);
+            if (kh == 0) {
+                const bool whole_row = (tile_first_kb == 0) && row_end;
+                const int n0 = nt * kTile + cg * 16 + gq;   // this lane's channels: n0 and n0 + 8
+                float v[NB][4];
+#pragma unroll
+                for (int nb = 0; nb < NB; ++nb) {
+                    const float4 o = *reinterpret_cast<const float4*>(&sm.fold[cg][nb][lane][0]);
+                    v[nb][0] = acc[nb][0] + o.x;
+                    v[nb][1] = acc[nb][1] + o.y;
+                    v[nb][2] = acc[nb][2] + o.z;
+                    v[nb][3] = acc[nb][3] + o.w;
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) acc[nb][c] = 0.f;
                 }
-                __threadfence();
-                consumer_bar();
-                if (threadIdx.x == 0) {
-                    const int contributed = kb + nb_tiles - tile_first_kb;
-                    const int old = atomicAdd(counter, contributed);
-                    sm.flag = (old + contributed == KT);
+                // fragment element c of group nb: token 8nb + 2tq + (c & 1), channel n0 + 8 * (c >> 1)
+                bool finalize = whole_row;
+                int* counter = reinterpret_cast<int*>(a.ws + (size_t)gridDim.y * 16 * a.N) +
+                               ((size_t)blockIdx.y * NT + nt) * 4 + cg;
+                // operands of the epilogue that do not depend on the sums: requested before the reduction
+                const float sc0 = __half2float(a.scale[n0]), sc1 = __half2float(a.scale[n0 + 8]);
+                __half res[NB][4];
+                if (a.epilogue == 1) {
+#pragma unroll
+                    for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+                        for (int c = 0; c < 4; ++c) {
+                            const int m = 8 * nb + 2 * tq + (c & 1);
+                            res[nb][c] = (m < rows) ? a.residual[(size_t)(m0 + m) * a.N + n0 + 8 * (c >> 1)]
+                                                    : __float2half(0.f);
+                        }
                 }
-                consumer_bar();
-                finalize = sm.flag != 0;
-                if (finalize) __threadfence();
-            }
-            if (finalize) {
-                for (int e = threadIdx.x; e < rows * 64; e += kConsumerThreads) {
-                    const int m = e >> 6, n = e & 63;
-                    float v;
-                    if (whole_row) {
-                        v = sm.tile[m][n];
+                if (!whole_row) {
+#pragma unroll
+                    for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+                        for (int c = 0; c < 4; ++c) {
+                            const int m = 8 * nb + 2 * tq + (c & 1);
+                            if (m < rows) atomicAdd(a.ws + (size_t)(m0 + m) * a.N + n0 + 8 * (c >> 1), v[nb][c]);
+                        }
+                    // one fence for the warp: the warp barrier orders the lanes' reductions before lane 0's
+                    // fence, which is cumulative (the pattern of a grid-wide barrier)
+                    __syncwarp();
+                    int last = 0;
+                    if (lane == 0) {
+                        __threadfence();
+                        const int contributed = kb + nb_tiles - tile_first_kb;
+                        const int old = atomicAdd(counter, contributed);
+                        last = (old + contributed == KT);
+                        if (last) __threadfence();
                     }
-                    else {
-                        v = __ldcg(ws_tile + (size_t)m * a.N + n);
-                        __stcg(ws_tile + (size_t)m * a.N + n, 0.f);
+                    last = __shfl_sync(0xffffffffu, last, 0);
+                    finalize = last != 0;
+                    if (finalize) {
+                        // all loads first, then all stores: the round trips to L2 overlap
+#pragma unroll
+                        for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+                            for (int c = 0; c < 4; ++c) {
+                                const int m = 8 * nb + 2 * tq + (c & 1);
+                                if (m < rows) v[nb][c] = __ldcg(a.ws + (size_t)(m0 + m) * a.N + n0 + 8 * (c >> 1));
+                            }
+#pragma unroll
+                        for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+                            for (int c = 0; c < 4; ++c) {
+                                const int m = 8 * nb + 2 * tq + (c & 1);
+                                if (m < rows) __stcg(a.ws + (size_t)(m0 + m) * a.N + n0 + 8 * (c >> 1), 0.f);
+                            }
+                        if (lane == 0) *counter = 0;
                     }
-                    const size_t o = (size_t)(m0 + m) * a.N + n_base + n;
-                    __half r = __float2half(v * __half2float(a.scale[n_base + n]));
-                    if (a.epilogue == 1) r = __hadd(r, a.residual[o]);
-                    a.C[o] = r;
                 }
-                if (!whole_row && threadIdx.x == 0) *counter = 0;
+                if (finalize) {
+#pragma unroll
+                    for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+                        for (int c = 0; c < 4; ++c) {
+                            const int m = 8 * nb + 2 * tq + (c & 1);
+                            if (m < rows) {
+                                __half r = __float2half(v[nb][c] * ((c >> 1) ? sc1 : sc0));
+                                if (a.epilogue == 1) r = __hadd(r, res[nb][c]);
+                                a.C[(size_t)(m0 + m) * a.N + n0 + 8 * (c >> 1)] = r;
+                            }
+                        }
+                }
             }
-            // each thread clears exactly the elements it read above (same e -> (m, n) mapping), so no
-            // barrier is needed between the reads and the clearing
-            for (int e = threadIdx.x; e < 16 * 64; e += kConsumerThreads) sm.tile[e >> 6][e & 63] = 0.f;
-            consumer_bar();
+            consumer_bar();   // the fold buffer may be rewritten by the next tile row
             tile_first_kb = -1;
         }
     }
@@ -278,7 +357,7 @@ size_t skinny_workspace_bytes(int M, int N, int dual)
     (void)dual;
     const size_t chunks = (size_t)((M + 15) / 16 > 0 ? (M + 15) / 16 : 1);
     const size_t chunks_per_launch = chunks < 8 ? chunks : 8;
-    return chunks_per_launch * 16 * (size_t)N * sizeof(float) + chunks_per_launch * (size_t)(N / kTile) * sizeof(int);
+    return chunks_per_launch * 16 * (size_t)N * sizeof(float) + chunks_per_launch * (size_t)(N / kTile) * 4 * sizeof(int);
 }
 
 int launch_gemm_skinny(const GemmArgs& a, cudaStream_t stream)
@@ -293,7 +372,6 @@ int launch_gemm_skinny(const GemmArgs& a, cudaStream_t stream)
     int grid_x = kSkinnyCtasPerSm * sm_count();
     if (grid_x > G) grid_x = (int)G;
     const int total_chunks = (a.M + 15) / 16;
-    const size_t smem = (size_t)kStages * kStageBytes;
     for (int c0 = 0; c0 < total_chunks; c0 += 8) {
         const int chunks = (total_chunks - c0 < 8) ? (total_chunks - c0) : 8;
         GemmArgs b = a;
@@ -304,6 +382,8 @@ int launch_gemm_skinny(const GemmArgs& a, cudaStream_t stream)
         if (b.M > chunks * 16) b.M = chunks * 16;
         const bool one_group = (b.M <= 8);
         auto kern = one_group ? gemm_skinny_kernel<1> : gemm_skinny_kernel<2>;
+        const int nbg = one_group ? 1 : 2;
+        const size_t smem = (size_t)stage_count(nbg) * stage_bytes(nbg);
         if (!attr_set[dev][one_group ? 0 : 1]) {
             EET_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
             attr_set[dev][one_group ? 0 : 1] = true;

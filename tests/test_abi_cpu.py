@@ -33,5 +33,5 @@ def test_argument_validation_happens_before_any_cuda_call():
     assert rc != 0 and b"NULL" in lib.eet_last_error()
     rc = lib.eet_decode_mha(None, None, None, None, 1, 1, 128, 8, 1, None, None, None, 0, None, 1, 10000.0, 0, None)
     assert rc != 0
-    assert lib.eet_gemm_w8a16_workspace_bytes(16, 4096, 4096) == 16 * 4096 * 4 + 64 * 4
+    assert lib.eet_gemm_w8a16_workspace_bytes(16, 4096, 4096) == 16 * 4096 * 4 + 64 * 4 * 4
     assert lib.eet_quantize_w8_workspace_bytes(4096, 11008) == 11008 * 4
