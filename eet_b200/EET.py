@@ -23,7 +23,8 @@ from . import _lib
 from ._lib import EETError, check, lib
 
 __all__ = ["MetaDesc", "LlamaMmha", "BaichuanMmha", "GatedFeedForwardNetworkInt8", "LayerNorm", "quant_weights",
-           "preprocess_weights", "unpack_weights", "repack_reference_weights", "gemm_w8a16", "EETError"]
+           "preprocess_weights", "unpack_weights", "repack_reference_weights", "gemm_w8a16", "gemm_w8a16_accum",
+           "deferred_epilogue", "EETError"]
 
 
 def _stream():
@@ -53,6 +54,16 @@ class _Pool:
         buf = self.buffers.get(key)
         if buf is None or buf.numel() < numel:
             buf = torch.empty(max(int(numel), 1), dtype=dtype, device=device)
+            self.buffers[key] = buf
+        return buf
+
+    def zeros(self, name, numel, dtype, device):
+        """Like get(), but zero-filled when (re)allocated: the fp32 sum buffers of the decode GEMMs, which
+        every reader leaves zero again."""
+        key = ("z:" + name, str(device), dtype)
+        buf = self.buffers.get(key)
+        if buf is None or buf.numel() < numel:
+            buf = torch.zeros(max(int(numel), 1), dtype=dtype, device=device)
             self.buffers[key] = buf
         return buf
 
@@ -206,6 +217,71 @@ def gemm_w8a16(x, packed_w, scale, out=None, residual=None):
     return out
 
 
+def gemm_w8a16_accum(x, packed_w, sums, packed_w2=None, sums2=None):
+    """sums[M, N] += x[M, K] @ q (unscaled int8 values); optionally the same for a second weight in the same
+    launch.  The decode-regime half of gemm_w8a16: whoever reads `sums` applies scale / residual."""
+    K, N = packed_w.shape
+    M = x.numel() // K
+    check(lib.eet_gemm_w8a16_accum(x.data_ptr(), packed_w.data_ptr(), sums.data_ptr(), M, N, K,
+                                   None if packed_w2 is None else packed_w2.data_ptr(),
+                                   None if sums2 is None else sums2.data_ptr(), _stream()))
+
+
+# ---------------------------------------------------------------------------------------------------
+# deferred epilogues (decode fast path)
+# ---------------------------------------------------------------------------------------------------
+class _Pending:
+    """An op output whose fp16 values do not exist yet: fp32 GEMM sums + scale + residual.  The next op of
+    this module that receives the tensor finishes it inside its own first kernel."""
+    __slots__ = ("sums", "scale", "residual", "out")
+
+    def __init__(self, sums, scale, residual, out):
+        self.sums, self.scale, self.residual, self.out = sums, scale, residual, out
+
+
+_pending = {}
+_defer = [False]
+_DECODE_MAX_M = 16
+
+
+class deferred_epilogue:
+    """Context manager for a chain of decode-step ops of this module (M <= 16, no tensor parallelism): inside
+    it an attention / FFN op returns its output tensor *before* the last GEMM's epilogue has run, and the next
+    op (attention, FFN or LayerNorm of this module) completes it in its RMSNorm kernel.  Outputs still
+    unfinished when the context ends are completed then, so callers outside never see stale memory."""
+
+    def __enter__(self):
+        self.prev = _defer[0]
+        _defer[0] = True
+        return self
+
+    def __exit__(self, *exc):
+        _defer[0] = self.prev
+        if not _defer[0]:
+            flush_pending()
+        return False
+
+
+def flush_pending():
+    for p in list(_pending.values()):
+        M, N = p.sums.shape
+        check(lib.eet_gemm_w8a16_finalize(p.sums.data_ptr(), p.scale.data_ptr(), _ptr(p.residual), p.out.data_ptr(),
+                                          M, N, _stream()))
+    _pending.clear()
+
+
+def _norm_head(x2d, gamma, eps, xn):
+    """RMSNorm at the head of a block; completes x first when it is a deferred output of the previous block."""
+    M, n = x2d.shape
+    p = _pending.pop(x2d.data_ptr(), None)
+    if p is not None:
+        check(lib.eet_rmsnorm_finalize(p.sums.data_ptr(), p.scale.data_ptr(), p.residual.data_ptr(), x2d.data_ptr(),
+                                       gamma.data_ptr(), xn.data_ptr(), M, n, eps, _stream()))
+    else:
+        check(lib.eet_rmsnorm(x2d.data_ptr(), gamma.data_ptr(), xn.data_ptr(), M, n, eps, _stream()))
+    return xn
+
+
 # ---------------------------------------------------------------------------------------------------
 # MetaDesc
 # ---------------------------------------------------------------------------------------------------
@@ -308,7 +384,12 @@ class _MmhaBase:
         out = _pool.get("self_mask_attn_cache", d.batch_size * d.max_seq_len * d.hidden_units, torch.float16, d.device)
         out = out[: B * S * d.hidden_units].view(B * S, d.hidden_units)
         inp2d = inp.reshape(B * S, d.hidden_units)
-        if d.tp is None or d.tp.size == 1:
+        if _defer[0] and B * S <= _DECODE_MAX_M and (d.tp is None or d.tp.size == 1):
+            sums = _pool.zeros("out_sums", d.batch_size * d.hidden_units, torch.float32, d.device)
+            sums = sums[: B * S * d.hidden_units].view(B * S, d.hidden_units)
+            gemm_w8a16_accum(ctx2d, self.out_w, sums)
+            _pending[out.data_ptr()] = _Pending(sums, self.out_s, inp2d, out)
+        elif d.tp is None or d.tp.size == 1:
             gemm_w8a16(ctx2d, self.out_w, self.out_s, out=out, residual=inp2d)
         else:
             gemm_w8a16(ctx2d, self.out_w, self.out_s, out=out)
@@ -347,7 +428,7 @@ class _MmhaBase:
         M = B * S
         cap = d.batch_size * d.max_seq_len
         xn = _pool.get("layernorm", cap * h, torch.float16, d.device)[: M * h].view(M, h)
-        _rmsnorm(inp.view(M, h), self.ln_w, d.layernorm_eps, xn)
+        _norm_head(inp.view(M, h), self.ln_w, d.layernorm_eps, xn)
         qkv = _pool.get("qkv_full", cap * 3 * self.inner_dim, torch.float16, d.device)[: M * 3 * self.inner_dim]
         qkv = qkv.view(M, 3 * self.inner_dim)
         gemm_w8a16(xn, self.qkv_w, self.qkv_s, out=qkv)
@@ -378,10 +459,17 @@ class _MmhaBase:
             raise RuntimeError("Exceed the maximum step length")
         H, D = d.head_num, self.size_per_head
         xn = _pool.get("layernorm_inc", d.batch_size * h, torch.float16, d.device)[: B * h].view(B, h)
-        _rmsnorm(inp.view(B, h), self.ln_w, d.layernorm_eps, xn)
-        qkv = _pool.get("qkv_inc", d.batch_size * 3 * self.inner_dim, torch.float16, d.device)
-        qkv = qkv[: B * 3 * self.inner_dim].view(B, 3 * self.inner_dim)
-        gemm_w8a16(xn, self.qkv_w, self.qkv_s, out=qkv)
+        _norm_head(inp.view(B, h), self.ln_w, d.layernorm_eps, xn)
+        qkv, qkv_sums = None, None
+        if _defer[0] and B <= _DECODE_MAX_M:
+            # the attention kernel finishes the projection itself: fp16(sums * scale)
+            qkv_sums = _pool.zeros("qkv_sums", d.batch_size * 3 * self.inner_dim, torch.float32, d.device)
+            qkv_sums = qkv_sums[: B * 3 * self.inner_dim].view(B, 3 * self.inner_dim)
+            gemm_w8a16_accum(xn, self.qkv_w, qkv_sums)
+        else:
+            qkv = _pool.get("qkv_inc", d.batch_size * 3 * self.inner_dim, torch.float16, d.device)
+            qkv = qkv[: B * 3 * self.inner_dim].view(B, 3 * self.inner_dim)
+            gemm_w8a16(xn, self.qkv_w, self.qkv_s, out=qkv)
         if reorder_state is not None and reorder_state.numel() != 0:
             self._reorder(reorder_state, B)
         ctx = _pool.get("context_buf", d.batch_size * self.inner_dim, torch.float16, d.device)[: B * self.inner_dim]
@@ -398,7 +486,8 @@ class _MmhaBase:
         step_dev = None
         if self.use_device_step:
             step_dev = self._arena.data_ptr() + 4 * self._slot
-        check(lib.eet_decode_mha(qkv.data_ptr(), self.k_cache.data_ptr(), self.v_cache.data_ptr(), ctx.data_ptr(),
+        check(lib.eet_decode_mha(_ptr(qkv), _ptr(qkv_sums), self.qkv_s.data_ptr(), self.k_cache.data_ptr(),
+                                 self.v_cache.data_ptr(), ctx.data_ptr(),
                                  B, H, D, d.max_full_seq_len, self.step_, step_dev, _ptr(pre_padding_len),
                                  _ptr(alibi), alibi_stride, _ptr(slopes), int(self.ROPE), self.rope_base, 0,
                                  _stream()))
@@ -487,15 +576,28 @@ class GatedFeedForwardNetworkInt8:
         cap = d.batch_size * d.max_seq_len
         with torch.cuda.device(d.device):
             xn = _pool.get("layernorm_tensor", cap * h, torch.float16, d.device)[: M * h].view(M, h)
-            _rmsnorm(input.view(M, h), self.ln_w, d.layernorm_eps, xn)
+            _norm_head(input.view(M, h), self.ln_w, d.layernorm_eps, xn)
             act = _pool.get("ffn_inner_act", cap * self.d_ff, torch.float16, d.device)[: M * self.d_ff].view(M, self.d_ff)
-            lin = _pool.get("ffn_inner_linear", cap * self.d_ff, torch.float16, d.device)[: M * self.d_ff].view(M, self.d_ff)
-            gemm_w8a16(xn, self.w0, self.s0, out=act)
-            gemm_w8a16(xn, self.w1, self.s1, out=lin)
-            check(lib.eet_swiglu(act.data_ptr(), lin.data_ptr(), M, self.d_ff, _stream()))
             out = _pool.get(self.cache_name, cap * h, torch.float16, d.device)[: M * h].view(M, h)
             inp2d = input.view(M, h)
-            if d.tp is None or d.tp.size == 1:
+            deferred = _defer[0] and M <= _DECODE_MAX_M
+            if deferred:
+                # gate and up in one launch, their epilogues inside the SwiGLU kernel
+                gs = _pool.zeros("gate_sums", d.batch_size * self.d_ff, torch.float32, d.device)[: M * self.d_ff].view(M, self.d_ff)
+                us = _pool.zeros("up_sums", d.batch_size * self.d_ff, torch.float32, d.device)[: M * self.d_ff].view(M, self.d_ff)
+                gemm_w8a16_accum(xn, self.w0, gs, self.w1, us)
+                check(lib.eet_swiglu_finalize(gs.data_ptr(), self.s0.data_ptr(), us.data_ptr(), self.s1.data_ptr(),
+                                              act.data_ptr(), M, self.d_ff, _stream()))
+            else:
+                lin = _pool.get("ffn_inner_linear", cap * self.d_ff, torch.float16, d.device)[: M * self.d_ff].view(M, self.d_ff)
+                gemm_w8a16(xn, self.w0, self.s0, out=act)
+                gemm_w8a16(xn, self.w1, self.s1, out=lin)
+                check(lib.eet_swiglu(act.data_ptr(), lin.data_ptr(), M, self.d_ff, _stream()))
+            if deferred and add_residual and (d.tp is None or d.tp.size == 1):
+                sums = _pool.zeros("down_sums", d.batch_size * h, torch.float32, d.device)[: M * h].view(M, h)
+                gemm_w8a16_accum(act, self.w_out, sums)
+                _pending[out.data_ptr()] = _Pending(sums, self.s_out, inp2d, out)
+            elif d.tp is None or d.tp.size == 1:
                 gemm_w8a16(act, self.w_out, self.s_out, out=out, residual=inp2d if add_residual else None)
             else:
                 gemm_w8a16(act, self.w_out, self.s_out, out=out)
@@ -529,7 +631,7 @@ class LayerNorm:
         B, S, h = input_tensor.shape
         out = self.output.view(-1)[: B * S * h].view(B * S, h)
         with torch.cuda.device(self.desc.device):
-            _rmsnorm(input_tensor.reshape(B * S, h), self.gamma, self.desc.layernorm_eps, out)
+            _norm_head(input_tensor.reshape(B * S, h), self.gamma, self.desc.layernorm_eps, out)
         return out.view(B, S, h)
 
 

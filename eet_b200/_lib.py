@@ -24,12 +24,16 @@ SIGNATURES = {
     "eet_repack_ref_w8": (_i, [_vp, _i, _i, _vp, _vp]),
     "eet_gemm_w8a16_workspace_bytes": (_sz, [_i, _i, _i]),
     "eet_gemm_w8a16": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _vp, _i, _vp, _sz, _vp]),
+    "eet_gemm_w8a16_accum": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp, _vp, _vp]),
+    "eet_gemm_w8a16_finalize": (_i, [_vp, _vp, _vp, _vp, _i, _i, _vp]),
+    "eet_rmsnorm_finalize": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _f, _vp]),
+    "eet_swiglu_finalize": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _vp]),
     "eet_rmsnorm": (_i, [_vp, _vp, _vp, _i, _i, _f, _vp]),
     "eet_swiglu": (_i, [_vp, _vp, _i, _i, _vp]),
     "eet_add_residual": (_i, [_vp, _vp, _sz, _vp]),
     "eet_qkv_split_store": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp]),
     "eet_prefill_mha": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, _i, _vp]),
-    "eet_decode_mha": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _i, _vp, _i, _f, _i, _vp]),
+    "eet_decode_mha": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _i, _vp, _i, _f, _i, _vp]),
     "eet_reorder_kv_workspace_bytes": (_sz, [_i, _i, _i, _i]),
     "eet_reorder_kv": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _sz, _vp]),
     "eet_advance_steps": (_i, [_vp, _i, _i, _vp]),

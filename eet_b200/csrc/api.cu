@@ -55,7 +55,7 @@ extern "C" {
 
 int eet_abi_version(void)
 {
-    return 1;
+    return 2;
 }
 
 const char* eet_last_error(void)
@@ -125,39 +125,81 @@ int eet_repack_ref_w8(const void* ref_packed, int K, int N, void* packed, void* 
     return launch_repack_ref_w8(ref_packed, K, N, packed, (cudaStream_t)stream);
 }
 
+static const int kSkinnyGroupRows = 128;  // rows finished per accumulate + finalize pair when M is large
+
 size_t eet_gemm_w8a16_workspace_bytes(int M, int N, int K)
 {
     (void)K;
-    if (N <= 0) return 0;
-    return skinny_workspace_bytes(M, N, 0);
+    if (N <= 0 || M <= 0) return 0;
+    return skinny_sum_bytes(M < kSkinnyGroupRows ? M : kSkinnyGroupRows, N);
+}
+
+static int check_gemm(const char* who, const void* A, const void* B, int M, int N, int K)
+{
+    if (check_kn(who, K, N)) return 1;
+    EET_CHECK(M >= 0, "%s: M=%d is negative", who, M);
+    EET_CHECK(M == 0 || (A && B), "%s: A and B must not be NULL", who);
+    EET_CHECK(aligned16(A) && aligned16(B), "%s: pointers must be 16-byte aligned", who);
+    return 0;
+}
+
+int eet_gemm_w8a16_accum(const void* A, const void* packedB, float* sums, int M, int N, int K, const void* packedB2,
+                         float* sums2, void* stream)
+{
+    if (check_gemm("eet_gemm_w8a16_accum", A, packedB, M, N, K)) return 1;
+    if (M == 0) return 0;
+    EET_CHECK(sums != nullptr && aligned16(sums), "eet_gemm_w8a16_accum: sums must be a 16-byte aligned buffer");
+    EET_CHECK((packedB2 == nullptr) == (sums2 == nullptr), "eet_gemm_w8a16_accum: B2 and sums2 go together");
+    EET_CHECK(aligned16(packedB2) && aligned16(sums2), "eet_gemm_w8a16_accum: pointers must be 16-byte aligned");
+    GemmArgs a = {};
+    a.A = (const __half*)A;
+    a.B = (const uint8_t*)packedB;
+    a.B2 = (const uint8_t*)packedB2;
+    a.ws = sums;
+    a.ws2 = sums2;
+    a.M = M;
+    a.N = N;
+    a.K = K;
+    return launch_gemm_skinny(a, (cudaStream_t)stream);
+}
+
+int eet_gemm_w8a16_finalize(float* sums, const void* scale, const void* residual, void* C, int M, int N, void* stream)
+{
+    EET_CHECK(M >= 0 && N > 0 && N % 8 == 0, "eet_gemm_w8a16_finalize: bad shape M=%d N=%d", M, N);
+    if (M == 0) return 0;
+    EET_CHECK(sums && scale && C, "eet_gemm_w8a16_finalize: sums, scale and C must not be NULL");
+    EET_CHECK(aligned16(sums) && aligned16(scale) && aligned16(C) && aligned16(residual),
+              "eet_gemm_w8a16_finalize: pointers must be 16-byte aligned");
+    return launch_finalize(sums, (const __half*)scale, (const __half*)residual, (__half*)C, M, N, (cudaStream_t)stream);
 }
 
 int eet_gemm_w8a16(const void* A, const void* packedB, const void* scale, void* C, int M, int N, int K,
                    const void* residual, int epilogue, void* ws, size_t ws_bytes, void* stream)
 {
-    if (check_kn("eet_gemm_w8a16", K, N)) return 1;
-    EET_CHECK(M >= 0, "eet_gemm_w8a16: M=%d is negative", M);
+    if (check_gemm("eet_gemm_w8a16", A, packedB, M, N, K)) return 1;
     if (M == 0) return 0;
-    EET_CHECK(A && packedB && scale && C, "eet_gemm_w8a16: A, B, scale and C must not be NULL");
-    EET_CHECK(aligned16(A) && aligned16(packedB) && aligned16(C), "eet_gemm_w8a16: pointers must be 16-byte aligned");
+    EET_CHECK(scale && C && aligned16(C) && aligned16(scale), "eet_gemm_w8a16: scale and C must be 16-byte aligned buffers");
     EET_CHECK(epilogue == 0 || epilogue == 1, "eet_gemm_w8a16: unknown epilogue %d", epilogue);
     EET_CHECK(epilogue != 1 || residual != nullptr, "eet_gemm_w8a16: epilogue 1 needs a residual");
-    EET_CHECK(ws && ws_bytes >= eet_gemm_w8a16_workspace_bytes(M, N, K),
+    EET_CHECK(ws && aligned16(ws) && ws_bytes >= eet_gemm_w8a16_workspace_bytes(M, N, K),
               "eet_gemm_w8a16: workspace of %zu bytes is smaller than the %zu needed", ws_bytes,
               eet_gemm_w8a16_workspace_bytes(M, N, K));
-    GemmArgs a = {};
-    a.A = (const __half*)A;
-    a.B = (const uint8_t*)packedB;
-    a.scale = (const __half*)scale;
-    a.C = (__half*)C;
-    a.residual = (const __half*)residual;
-    a.M = M;
-    a.N = N;
-    a.K = K;
-    a.epilogue = epilogue;
-    a.ws = (float*)ws;
-    a.ws_bytes = ws_bytes;
-    return launch_gemm_skinny(a, (cudaStream_t)stream);
+    const __half* res = epilogue == 1 ? (const __half*)residual : nullptr;
+    for (int r0 = 0; r0 < M; r0 += kSkinnyGroupRows) {
+        const int rows = (M - r0 < kSkinnyGroupRows) ? (M - r0) : kSkinnyGroupRows;
+        GemmArgs a = {};
+        a.A = (const __half*)A + (size_t)r0 * K;
+        a.B = (const uint8_t*)packedB;
+        a.ws = (float*)ws;
+        a.M = rows;
+        a.N = N;
+        a.K = K;
+        if (int rc = launch_gemm_skinny(a, (cudaStream_t)stream)) return rc;
+        if (int rc = launch_finalize((float*)ws, (const __half*)scale, res ? res + (size_t)r0 * N : nullptr,
+                                     (__half*)C + (size_t)r0 * N, rows, N, (cudaStream_t)stream))
+            return rc;
+    }
+    return 0;
 }
 
 int eet_rmsnorm(const void* x, const void* gamma, void* y, int M, int n, float eps, void* stream)
@@ -165,6 +207,30 @@ int eet_rmsnorm(const void* x, const void* gamma, void* y, int M, int n, float e
     EET_CHECK(M >= 0 && x && gamma && y, "eet_rmsnorm: bad arguments");
     EET_CHECK(aligned16(x) && aligned16(gamma) && aligned16(y), "eet_rmsnorm: pointers must be 16-byte aligned");
     return launch_rmsnorm((const __half*)x, (const __half*)gamma, (__half*)y, M, n, eps, (cudaStream_t)stream);
+}
+
+int eet_rmsnorm_finalize(float* sums, const void* scale, const void* residual, void* h_out, const void* gamma,
+                         void* xn_out, int M, int n, float eps, void* stream)
+{
+    EET_CHECK(M >= 0 && residual && gamma && xn_out, "eet_rmsnorm_finalize: bad arguments");
+    EET_CHECK(sums == nullptr || (scale != nullptr && h_out != nullptr),
+              "eet_rmsnorm_finalize: sums need their scale and an output for the finished rows");
+    EET_CHECK(aligned16(sums) && aligned16(scale) && aligned16(residual) && aligned16(h_out) && aligned16(gamma) &&
+                  aligned16(xn_out),
+              "eet_rmsnorm_finalize: pointers must be 16-byte aligned");
+    return launch_rmsnorm_finalize(sums, (const __half*)scale, (const __half*)residual, (__half*)h_out,
+                                   (const __half*)gamma, (__half*)xn_out, M, n, eps, (cudaStream_t)stream);
+}
+
+int eet_swiglu_finalize(float* gate_sums, const void* gate_scale, float* up_sums, const void* up_scale, void* act_out,
+                        int M, int n, void* stream)
+{
+    EET_CHECK(M >= 0 && gate_sums && gate_scale && up_sums && up_scale && act_out, "eet_swiglu_finalize: bad arguments");
+    EET_CHECK(aligned16(gate_sums) && aligned16(gate_scale) && aligned16(up_sums) && aligned16(up_scale) &&
+                  aligned16(act_out),
+              "eet_swiglu_finalize: pointers must be 16-byte aligned");
+    return launch_swiglu_finalize(gate_sums, (const __half*)gate_scale, up_sums, (const __half*)up_scale,
+                                  (__half*)act_out, M, n, (cudaStream_t)stream);
 }
 
 int eet_swiglu(void* gate_inout, const void* up, int M, int n, void* stream)
@@ -197,15 +263,20 @@ int eet_prefill_mha(const void* q, const void* kcache, const void* vcache, void*
                               T_max, pad_len, (const __half*)alibi, alibi_stride, (cudaStream_t)stream);
 }
 
-int eet_decode_mha(const void* qkv, void* kcache, void* vcache, void* ctx, int B, int H, int D, int T_max, int step,
-                   const int* step_dev, const int64_t* pad_len, const void* alibi, int alibi_stride,
-                   const float* alibi_slopes, int rope, float rope_base, int splits, void* stream)
+int eet_decode_mha(const void* qkv, float* qkv_sums, const void* qkv_scale, void* kcache, void* vcache, void* ctx,
+                   int B, int H, int D, int T_max, int step, const int* step_dev, const int64_t* pad_len,
+                   const void* alibi, int alibi_stride, const float* alibi_slopes, int rope, float rope_base, int splits,
+                   void* stream)
 {
-    EET_CHECK(qkv && kcache && vcache && ctx && B >= 0 && H > 0, "eet_decode_mha: bad arguments");
-    EET_CHECK(aligned16(qkv) && aligned16(kcache) && aligned16(vcache) && aligned16(ctx),
+    EET_CHECK(kcache && vcache && ctx && B >= 0 && H > 0, "eet_decode_mha: bad arguments");
+    EET_CHECK((qkv != nullptr) != (qkv_sums != nullptr), "eet_decode_mha: pass either qkv or qkv_sums");
+    EET_CHECK(qkv_sums == nullptr || qkv_scale != nullptr, "eet_decode_mha: qkv_sums need qkv_scale");
+    EET_CHECK(aligned16(qkv) && aligned16(qkv_sums) && aligned16(kcache) && aligned16(vcache) && aligned16(ctx),
               "eet_decode_mha: pointers must be 16-byte aligned");
     DecodeAttnArgs a = {};
     a.qkv = (const __half*)qkv;
+    a.qkv_sums = qkv_sums;
+    a.qkv_scale = (const __half*)qkv_scale;
     a.kcache = (__half*)kcache;
     a.vcache = (__half*)vcache;
     a.ctx = (__half*)ctx;

@@ -104,14 +104,22 @@ decode_mha_kernel(DecodeAttnArgs a)
     pdl_wait();
     const int step = a.step_dev ? *a.step_dev : a.step;
     const size_t inner = (size_t)a.H * D;
-    const __half* qkv = a.qkv + (size_t)b * 3 * inner + (size_t)h * D;
 
     // ---- new token: rotate q,k at position step-1, round to fp16 as the reference's buffers do ----
+    // The projection arrives either as fp16 [B][3][H][D] or as the fp32 sums of the skinny GEMM, which are
+    // finished here: fp16(sum * scale), the value the reference's GEMM epilogue would have stored.
+    auto proj = [&](int which, int i) -> __half {
+        const size_t col = (size_t)which * inner + (size_t)h * D + i;
+        if (a.qkv_sums != nullptr) {
+            return __float2half(__ldcg(a.qkv_sums + (size_t)b * 3 * inner + col) * __half2float(a.qkv_scale[col]));
+        }
+        return a.qkv[(size_t)b * 3 * inner + col];
+    };
     if (tid < D / 2) {
         const int i = tid;
-        float q1 = __half2float(qkv[i]), q2 = __half2float(qkv[i + D / 2]);
-        float k1 = __half2float(qkv[inner + i]), k2 = __half2float(qkv[inner + i + D / 2]);
+        const __half hq1 = proj(0, i), hq2 = proj(0, i + D / 2), hk1 = proj(1, i), hk2 = proj(1, i + D / 2);
         if (a.rope) {
+            const float q1 = __half2float(hq1), q2 = __half2float(hq2), k1 = __half2float(hk1), k2 = __half2float(hk2);
             const float ang = (float)(step - 1) / powf(a.rope_base, (float)(2 * i) / (float)D);
             const float c = cosf(ang), sn = sinf(ang);
             s_q[i] = __float2half(q1 * c - q2 * sn);
@@ -120,16 +128,16 @@ decode_mha_kernel(DecodeAttnArgs a)
             s_k[i + D / 2] = __float2half(k2 * c + k1 * sn);
         }
         else {
-            s_q[i] = qkv[i];
-            s_q[i + D / 2] = qkv[i + D / 2];
-            s_k[i] = qkv[inner + i];
-            s_k[i + D / 2] = qkv[inner + i + D / 2];
+            s_q[i] = hq1;
+            s_q[i + D / 2] = hq2;
+            s_k[i] = hk1;
+            s_k[i + D / 2] = hk2;
         }
     }
     else if (tid < D) {
         const int i = tid - D / 2;
-        s_v[i] = qkv[2 * inner + i];
-        s_v[i + D / 2] = qkv[2 * inner + i + D / 2];
+        s_v[i] = proj(2, i);
+        s_v[i + D / 2] = proj(2, i + D / 2);
     }
     __syncthreads();
 
@@ -240,6 +248,12 @@ decode_mha_kernel(DecodeAttnArgs a)
 
     // ---- merge the CTAs of the cluster; rank 0 writes the context ----
     cluster.sync();
+    if (split == 0 && a.qkv_sums != nullptr) {
+        // every CTA of the cluster has read the projection sums of this (batch, head): put them back to zero
+        for (int e = tid; e < 3 * D; e += kAttnThreads) {
+            __stcg(a.qkv_sums + (size_t)b * 3 * inner + (size_t)(e / D) * inner + (size_t)h * D + (e % D), 0.f);
+        }
+    }
     if (split == 0 && tid < D) {
         float m = -1e20f;
         for (int r = 0; r < splits; ++r) {

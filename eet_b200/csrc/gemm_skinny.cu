@@ -19,18 +19,23 @@
 //    bytes become fp16 in registers (prmt + sub.f16x2) and feed the tensor cores with up to 8 tokens as
 //    the B operand; the reduction index is permuted identically on both operands, so no shuffles or
 //    transposes are needed, and a warp's accumulators stay in registers for a whole tile row.
-//  * When a CTA's run ends inside a tile row, partial sums go to an fp32 scratch with red.global.add and
-//    an arrival counter per 16 channels; the warp that completes the count applies the scale (and
-//    residual), writes fp16, and restores the scratch to zero.  Tile rows covered by one CTA skip the
-//    scratch.
+//  * The kernel's result is the fp32 sum over k of x[m][k] * q[k][n], ADDED into a caller-provided fp32
+//    buffer with red.global.add at the end of each CTA's share of a tile row (one to three CTAs
+//    contribute to a row).  Scale, residual and the fp16 rounding are left to whoever reads the sums -
+//    the generic finalize kernel below, or the next kernel of a decode step (RMSNorm, attention, SwiGLU),
+//    which also puts the buffer back to zero.  Nothing in this kernel waits on another CTA.
 //  * Programmatic dependent launch: the kernel may start while its predecessor in the stream is still
 //    draining.  Weights do not depend on earlier kernels, so the producer streams them at once; only the
 //    consumers wait (griddepcontrol.wait) before they touch activations, scratch or the output.  Back to
 //    back GEMMs of a decode step therefore keep HBM busy across kernel boundaries.
 //
-// Numerics: products of fp16 activations with exact integer weights, fp32 accumulation, one multiply by
-// the fp16 scale, one rounding to fp16 (the reference rounds every q*scale to fp16 first and rounds the
-// fp32 accumulator once: mma_tensorop_dequantizer.h:259-274, epilogue_helpers.h:73-80).
+//  * Two weight matrices with the same K and N (the gate and up projections of the FFN) can be walked by
+//    one launch: the tile list is the concatenation of both and each has its own sum buffer.
+//
+// Numerics: products of fp16 activations with exact integer weights, fp32 accumulation; the finalize step
+// multiplies once by the fp16 scale and rounds once to fp16 (the reference rounds every q*scale to fp16
+// first and rounds the fp32 accumulator once: mma_tensorop_dequantizer.h:259-274,
+// epilogue_helpers.h:73-80).
 #include "common.cuh"
 #include "kernels.h"
 
@@ -80,7 +85,8 @@ gemm_skinny_kernel(GemmArgs a)
     pdl_launch_dependents();
 
     const int KT = a.K / kTile, NT = a.N / kTile;
-    const long long G = (long long)NT * KT;
+    const long long G1 = (long long)NT * KT;               // tiles of one matrix
+    const long long G = a.B2 ? 2 * G1 : G1;
     const int g0 = (int)(G * blockIdx.x / gridDim.x);
     const int g1 = (int)(G * (blockIdx.x + 1) / gridDim.x);
     const int m0 = blockIdx.y * 16;
@@ -115,8 +121,9 @@ gemm_skinny_kernel(GemmArgs a)
                     }
                 }
                 mbar_arrive_expect_tx(&sm.full[s], (uint32_t)(nb_tiles * kTileBytes));
-                bulk_g2s_stream(dyn_smem + (size_t)s * kStageBytes, a.B + (size_t)g * kTileBytes,
-                                (uint32_t)(nb_tiles * kTileBytes), &sm.full[s]);
+                const uint8_t* src = (g < G1) ? a.B + (size_t)g * kTileBytes : a.B2 + (size_t)(g - G1) * kTileBytes;
+                bulk_g2s_stream(dyn_smem + (size_t)s * kStageBytes, src, (uint32_t)(nb_tiles * kTileBytes),
+                                &sm.full[s]);
                 g += nb_tiles;
             }
         }
@@ -166,7 +173,6 @@ gemm_skinny_kernel(GemmArgs a)
 
     // schedule walk shared with the producer: stage `it` holds tiles [g, g + nb_tiles) of one tile row
     int it = 0;
-    int tile_first_kb = -1;  // first k-tile of the current tile row handled by this CTA
     if (g0 < g1) {
         const int nt = g0 / KT, kb = g0 - nt * KT;
         fetch_x(kb, min(min(kStageTiles, KT - kb), g1 - g0));
@@ -175,7 +181,6 @@ gemm_skinny_kernel(GemmArgs a)
         const int nt = g / KT, kb = g - nt * KT;
         const int nb_tiles = min(min(kStageTiles, KT - kb), g1 - g);
         const int s = it % kStages;
-        if (tile_first_kb < 0) tile_first_kb = kb;
         {
             uint8_t* xdst = dyn_smem + (size_t)s * kStageBytes + kStageWBytes + kh * kHalfTiles * 128;
 #pragma unroll
@@ -260,115 +265,42 @@ gemm_skinny_kernel(GemmArgs a)
             }
             consumer_bar();
             if (kh == 0) {
-                const bool whole_row = (tile_first_kb == 0) && row_end;
-                const int n0 = nt * kTile + cg * 16 + gq;   // this lane's channels: n0 and n0 + 8
-                float v[NB][4];
+                // fragment element c of group nb: token 8nb + 2tq + (c & 1), channel n0 + 8 * (c >> 1)
+                float* sums = (nt < NT) ? a.ws : a.ws2;
+                const int n0 = (nt < NT ? nt : nt - NT) * kTile + cg * 16 + gq;
 #pragma unroll
                 for (int nb = 0; nb < NB; ++nb) {
                     const float4 o = *reinterpret_cast<const float4*>(&sm.fold[cg][nb][lane][0]);
-                    v[nb][0] = acc[nb][0] + o.x;
-                    v[nb][1] = acc[nb][1] + o.y;
-                    v[nb][2] = acc[nb][2] + o.z;
-                    v[nb][3] = acc[nb][3] + o.w;
+                    const float v[4] = {acc[nb][0] + o.x, acc[nb][1] + o.y, acc[nb][2] + o.z, acc[nb][3] + o.w};
 #pragma unroll
-                    for (int c = 0; c < 4; ++c) acc[nb][c] = 0.f;
-                }
-                // fragment element c of group nb: token 8nb + 2tq + (c & 1), channel n0 + 8 * (c >> 1)
-                bool finalize = whole_row;
-                int* counter = reinterpret_cast<int*>(a.ws + (size_t)gridDim.y * 16 * a.N) +
-                               ((size_t)blockIdx.y * NT + nt) * 4 + cg;
-                // operands of the epilogue that do not depend on the sums: requested before the reduction
-                const float sc0 = __half2float(a.scale[n0]), sc1 = __half2float(a.scale[n0 + 8]);
-                __half res[NB][4];
-                if (a.epilogue == 1) {
-#pragma unroll
-                    for (int nb = 0; nb < NB; ++nb)
-#pragma unroll
-                        for (int c = 0; c < 4; ++c) {
-                            const int m = 8 * nb + 2 * tq + (c & 1);
-                            res[nb][c] = (m < rows) ? a.residual[(size_t)(m0 + m) * a.N + n0 + 8 * (c >> 1)]
-                                                    : __float2half(0.f);
-                        }
-                }
-                if (!whole_row) {
-#pragma unroll
-                    for (int nb = 0; nb < NB; ++nb)
-#pragma unroll
-                        for (int c = 0; c < 4; ++c) {
-                            const int m = 8 * nb + 2 * tq + (c & 1);
-                            if (m < rows) atomicAdd(a.ws + (size_t)(m0 + m) * a.N + n0 + 8 * (c >> 1), v[nb][c]);
-                        }
-                    // one fence for the warp: the warp barrier orders the lanes' reductions before lane 0's
-                    // fence, which is cumulative (the pattern of a grid-wide barrier)
-                    __syncwarp();
-                    int last = 0;
-                    if (lane == 0) {
-                        __threadfence();
-                        const int contributed = kb + nb_tiles - tile_first_kb;
-                        const int old = atomicAdd(counter, contributed);
-                        last = (old + contributed == KT);
-                        if (last) __threadfence();
+                    for (int c = 0; c < 4; ++c) {
+                        const int m = 8 * nb + 2 * tq + (c & 1);
+                        if (m < rows) atomicAdd(sums + (size_t)(m0 + m) * a.N + n0 + 8 * (c >> 1), v[c]);
+                        acc[nb][c] = 0.f;
                     }
-                    last = __shfl_sync(0xffffffffu, last, 0);
-                    finalize = last != 0;
-                    if (finalize) {
-                        // all loads first, then all stores: the round trips to L2 overlap
-#pragma unroll
-                        for (int nb = 0; nb < NB; ++nb)
-#pragma unroll
-                            for (int c = 0; c < 4; ++c) {
-                                const int m = 8 * nb + 2 * tq + (c & 1);
-                                if (m < rows) v[nb][c] = __ldcg(a.ws + (size_t)(m0 + m) * a.N + n0 + 8 * (c >> 1));
-                            }
-#pragma unroll
-                        for (int nb = 0; nb < NB; ++nb)
-#pragma unroll
-                            for (int c = 0; c < 4; ++c) {
-                                const int m = 8 * nb + 2 * tq + (c & 1);
-                                if (m < rows) __stcg(a.ws + (size_t)(m0 + m) * a.N + n0 + 8 * (c >> 1), 0.f);
-                            }
-                        if (lane == 0) *counter = 0;
-                    }
-                }
-                if (finalize) {
-#pragma unroll
-                    for (int nb = 0; nb < NB; ++nb)
-#pragma unroll
-                        for (int c = 0; c < 4; ++c) {
-                            const int m = 8 * nb + 2 * tq + (c & 1);
-                            if (m < rows) {
-                                __half r = __float2half(v[nb][c] * ((c >> 1) ? sc1 : sc0));
-                                if (a.epilogue == 1) r = __hadd(r, res[nb][c]);
-                                a.C[(size_t)(m0 + m) * a.N + n0 + 8 * (c >> 1)] = r;
-                            }
-                        }
                 }
             }
             consumer_bar();   // the fold buffer may be rewritten by the next tile row
-            tile_first_kb = -1;
         }
     }
 }
 
 }  // namespace
 
-size_t skinny_workspace_bytes(int M, int N, int dual)
+size_t skinny_sum_bytes(int M, int N)
 {
-    (void)dual;
-    const size_t chunks = (size_t)((M + 15) / 16 > 0 ? (M + 15) / 16 : 1);
-    const size_t chunks_per_launch = chunks < 8 ? chunks : 8;
-    return chunks_per_launch * 16 * (size_t)N * sizeof(float) + chunks_per_launch * (size_t)(N / kTile) * 4 * sizeof(int);
+    return (size_t)(M > 0 ? M : 0) * (size_t)N * sizeof(float);
 }
 
+// Adds A[M,K] x q(B) (and, with B2, A x q(B2)) into the fp32 buffers sums (sums2), rows [0, M).
 int launch_gemm_skinny(const GemmArgs& a, cudaStream_t stream)
 {
-    EET_CHECK(a.epilogue == 0 || a.epilogue == 1, "skinny GEMM: epilogue %d is not supported", a.epilogue);
     if (a.M == 0) return 0;
     static bool attr_set[64][2] = {};
     int dev = 0;
     EET_CUDA(cudaGetDevice(&dev));
     dev &= 63;
-    const long long G = (long long)(a.N / kTile) * (a.K / kTile);
+    const long long G = (long long)(a.N / kTile) * (a.K / kTile) * (a.B2 ? 2 : 1);
     int grid_x = kSkinnyCtasPerSm * sm_count();
     if (grid_x > G) grid_x = (int)G;
     const int total_chunks = (a.M + 15) / 16;
@@ -376,8 +308,8 @@ int launch_gemm_skinny(const GemmArgs& a, cudaStream_t stream)
         const int chunks = (total_chunks - c0 < 8) ? (total_chunks - c0) : 8;
         GemmArgs b = a;
         b.A = a.A + (size_t)c0 * 16 * a.K;
-        b.C = a.C + (size_t)c0 * 16 * a.N;
-        if (a.residual) b.residual = a.residual + (size_t)c0 * 16 * a.N;
+        b.ws = a.ws + (size_t)c0 * 16 * a.N;
+        if (a.ws2) b.ws2 = a.ws2 + (size_t)c0 * 16 * a.N;
         b.M = a.M - c0 * 16;
         if (b.M > chunks * 16) b.M = chunks * 16;
         const bool one_group = (b.M <= 8);

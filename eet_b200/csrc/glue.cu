@@ -71,6 +71,128 @@ rmsnorm_kernel(const __half* __restrict__ x, const __half* __restrict__ gamma, _
     }
 }
 
+// ---- consumers of the skinny GEMM's fp32 sums -------------------------------------------------------
+// The decode-regime GEMM leaves sum_k x[m][k] * q[k][n] in an fp32 buffer; what the reference's GEMM
+// epilogue does next (multiply by the per-channel scale, round once to fp16: epilogue_helpers.h:73-80) and
+// what its add_input kernel does after that (fp16 add of the residual, csrc/core/add_bias.cu:22-28) happen
+// in the kernel that reads the sums.  Every reader restores the buffer to zero for the next GEMM.
+
+__device__ __forceinline__ void load_sums8(float* p, float (&v)[8])
+{
+    const float4 a = __ldcg(reinterpret_cast<const float4*>(p));
+    const float4 b = __ldcg(reinterpret_cast<const float4*>(p) + 1);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+    v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+    __stcg(reinterpret_cast<float4*>(p), z);
+    __stcg(reinterpret_cast<float4*>(p) + 1, z);
+}
+
+// 8 outputs: fp16(sum * scale) (+ residual in fp16)
+__device__ __forceinline__ uint4 finalize8(const float (&v)[8], const uint4& scale, const uint4* residual)
+{
+    const __half2* sh = reinterpret_cast<const __half2*>(&scale);
+    uint4 o;
+    __half2* oh = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        const float2 sc = __half22float2(sh[e]);
+        oh[e] = __floats2half2_rn(v[2 * e] * sc.x, v[2 * e + 1] * sc.y);
+    }
+    if (residual != nullptr) {
+        const __half2* rh = reinterpret_cast<const __half2*>(residual);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) oh[e] = __hadd2(oh[e], rh[e]);
+    }
+    return o;
+}
+
+// C = fp16(sums * scale) (+ residual); sums <- 0.
+__global__ void __launch_bounds__(256)
+finalize_kernel(float* __restrict__ sums, const __half* __restrict__ scale, const __half* __restrict__ residual,
+                __half* __restrict__ C, int N, size_t nvec)
+{
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= nvec) return;
+    const int col = (int)((i * 8) % (size_t)N);
+    float v[8];
+    load_sums8(sums + i * 8, v);
+    const uint4 sc = *reinterpret_cast<const uint4*>(scale + col);
+    uint4 r;
+    if (residual != nullptr) r = reinterpret_cast<const uint4*>(residual)[i];
+    reinterpret_cast<uint4*>(C)[i] = finalize8(v, sc, residual ? &r : nullptr);
+}
+
+// Row kernel at the head of an attention or FFN block during decode.  With sums != null it first finishes
+// the projection GEMM that produced this block's input: h = fp16(sums * scale) + residual, written to
+// h_out as the new residual stream; with sums == null the input is `residual` itself.  Then
+// xn = h * rsqrt(mean(h^2) + eps) * gamma as in rmsnorm_kernel above.
+__global__ void __launch_bounds__(1024)
+rmsnorm_finalize_kernel(float* __restrict__ sums, const __half* __restrict__ scale, const __half* __restrict__ residual,
+                        __half* __restrict__ h_out, const __half* __restrict__ gamma, __half* __restrict__ xn_out, int n,
+                        float eps)
+{
+    __shared__ float red[32];
+    __shared__ float s_inv;
+    pdl_launch_dependents();
+    pdl_wait();
+    const int row = blockIdx.x;
+    const int nv = n >> 3;
+    const uint4* rr = reinterpret_cast<const uint4*>(residual + (size_t)row * n);
+    uint4 h[2];
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+        const int i = threadIdx.x + j * blockDim.x;
+        if (i < nv) {
+            h[j] = rr[i];
+            if (sums != nullptr) {
+                float v[8];
+                load_sums8(sums + (size_t)row * n + (size_t)i * 8, v);
+                const uint4 sc = reinterpret_cast<const uint4*>(scale)[i];
+                h[j] = finalize8(v, sc, &h[j]);
+                reinterpret_cast<uint4*>(h_out + (size_t)row * n)[i] = h[j];
+            }
+            const __half2* hh = reinterpret_cast<const __half2*>(&h[j]);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float2 f = __half22float2(hh[e]);
+                ss += f.x * f.x + f.y * f.y;
+            }
+        }
+    }
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        float t = (threadIdx.x < (blockDim.x >> 5)) ? red[threadIdx.x] : 0.f;
+        t = warp_sum(t);
+        if (threadIdx.x == 0) s_inv = rsqrtf(t / n + eps);
+    }
+    __syncthreads();
+    const float inv = s_inv;
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+        const int i = threadIdx.x + j * blockDim.x;
+        if (i < nv) {
+            const uint4 g = reinterpret_cast<const uint4*>(gamma)[i];
+            const __half2* hh = reinterpret_cast<const __half2*>(&h[j]);
+            const __half2* gh = reinterpret_cast<const __half2*>(&g);
+            uint4 o;
+            __half2* oh = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float2 f = __half22float2(hh[e]);
+                const float2 gg = __half22float2(gh[e]);
+                oh[e] = __float22half2_rn(make_float2(f.x * inv * gg.x, f.y * inv * gg.y));
+            }
+            reinterpret_cast<uint4*>(xn_out + (size_t)row * n)[i] = o;
+        }
+    }
+}
+
 // gate <- up * gate / (1 + exp(-gate)) with the reference's mix of precisions: exp in fp32 rounded to
 // fp16, the multiply, add and divide in fp16 (gated_silu<half>, csrc/core/activation_kernel.cu:106-124).
 __device__ __forceinline__ __half2 gated_silu2(__half2 g, __half2 u)
@@ -95,6 +217,30 @@ swiglu_kernel(__half* __restrict__ gate, const __half* __restrict__ up, size_t n
 #pragma unroll
     for (int e = 0; e < 4; ++e) gh[e] = gated_silu2(gh[e], uh[e]);
     reinterpret_cast<uint4*>(gate)[i] = g;
+}
+
+// act = gated_silu(fp16(gate_sums * gate_scale), fp16(up_sums * up_scale)); both sum buffers <- 0.
+__global__ void __launch_bounds__(256)
+swiglu_finalize_kernel(float* __restrict__ gate_sums, const __half* __restrict__ gate_scale, float* __restrict__ up_sums,
+                       const __half* __restrict__ up_scale, __half* __restrict__ act, int n, size_t nvec)
+{
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= nvec) return;
+    const int col = (int)((i * 8) % (size_t)n);
+    float gv[8], uv[8];
+    load_sums8(gate_sums + i * 8, gv);
+    load_sums8(up_sums + i * 8, uv);
+    const uint4 g = finalize8(gv, *reinterpret_cast<const uint4*>(gate_scale + col), nullptr);
+    const uint4 u = finalize8(uv, *reinterpret_cast<const uint4*>(up_scale + col), nullptr);
+    const __half2* gh = reinterpret_cast<const __half2*>(&g);
+    const __half2* uh = reinterpret_cast<const __half2*>(&u);
+    uint4 o;
+    __half2* oh = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) oh[e] = gated_silu2(gh[e], uh[e]);
+    reinterpret_cast<uint4*>(act)[i] = o;
 }
 
 // out += in in fp16 (add_input<half>, csrc/core/add_bias.cu:22-28).
@@ -210,6 +356,42 @@ int launch_rmsnorm(const __half* x, const __half* gamma, __half* y, int M, int n
     if (threads < 32) threads = 32;
     if (threads > 1024) threads = 1024;
     EET_CUDA(launch_pdl(rmsnorm_kernel, dim3(M), dim3(threads), 0, stream, x, gamma, y, n, eps));
+    return 0;
+}
+
+int launch_finalize(float* sums, const __half* scale, const __half* residual, __half* C, int M, int N,
+                    cudaStream_t stream)
+{
+    EET_CHECK(N % 8 == 0, "finalize: N must be a multiple of 8");
+    const size_t nvec = (size_t)M * N / 8;
+    if (nvec == 0) return 0;
+    EET_CUDA(launch_pdl(finalize_kernel, dim3((unsigned)((nvec + 255) / 256)), dim3(256), 0, stream, sums, scale,
+                        residual, C, N, nvec));
+    return 0;
+}
+
+int launch_rmsnorm_finalize(float* sums, const __half* scale, const __half* residual, __half* h_out,
+                            const __half* gamma, __half* xn_out, int M, int n, float eps, cudaStream_t stream)
+{
+    EET_CHECK(n % 8 == 0 && n > 0 && n <= 16384, "rmsnorm: hidden size %d must be a multiple of 8 and <= 16384", n);
+    if (M == 0) return 0;
+    const int nv = n / 8;
+    int threads = ((nv + 1) / 2 + 31) / 32 * 32;
+    if (threads < 32) threads = 32;
+    if (threads > 1024) threads = 1024;
+    EET_CUDA(launch_pdl(rmsnorm_finalize_kernel, dim3(M), dim3(threads), 0, stream, sums, scale, residual, h_out, gamma,
+                        xn_out, n, eps));
+    return 0;
+}
+
+int launch_swiglu_finalize(float* gate_sums, const __half* gate_scale, float* up_sums, const __half* up_scale,
+                           __half* act_out, int M, int n, cudaStream_t stream)
+{
+    EET_CHECK(n % 8 == 0, "swiglu: inner size %d must be a multiple of 8", n);
+    const size_t nvec = (size_t)M * n / 8;
+    if (nvec == 0) return 0;
+    EET_CUDA(launch_pdl(swiglu_finalize_kernel, dim3((unsigned)((nvec + 255) / 256)), dim3(256), 0, stream, gate_sums,
+                        gate_scale, up_sums, up_scale, act_out, n, nvec));
     return 0;
 }
 

@@ -18,26 +18,28 @@ int launch_repack_ref_w8(const void* ref_packed, int K, int N, void* packed, cud
 
 // gemm_skinny.cu
 struct GemmArgs {
-    const __half* A;         // [M][K]
-    const uint8_t* B;        // W8T64 [N/64][K/64][64][64]
-    const __half* scale;     // [N]
-    __half* C;               // [M][N]
-    const __half* residual;  // [M][N] or null; added in fp16 after the product was rounded to fp16
-    const uint8_t* B2;       // second weight (SwiGLU "up") or null
-    const __half* scale2;
+    const __half* A;    // [M][K] fp16 activations
+    const uint8_t* B;   // W8T64 [N/64][K/64][64][64]
+    const uint8_t* B2;  // optional second weight of the same shape (FFN up projection) or null
+    float* ws;          // [M][N] fp32: sum over k of A[m][k] * q[k][n] is ADDED here
+    float* ws2;         // the same for B2
     int M, N, K;
-    int epilogue;            // 0 plain, 1 + residual, 2 silu(A.B) * (A.B2)
-    float* ws;               // split-K accumulation scratch (zero on entry, left zero on exit)
-    size_t ws_bytes;
 };
-size_t skinny_workspace_bytes(int M, int N, int dual);
+size_t skinny_sum_bytes(int M, int N);
 int launch_gemm_skinny(const GemmArgs& a, cudaStream_t stream);
 
 // gemm_tc.cu (tcgen05 / TMEM)
-int launch_gemm_tc(const GemmArgs& a, cudaStream_t stream);
+int launch_gemm_tc(const __half* A, const uint8_t* B, const __half* scale, __half* C, const __half* residual, int M,
+                   int N, int K, cudaStream_t stream);
 
 // glue.cu
 int launch_rmsnorm(const __half* x, const __half* gamma, __half* y, int M, int n, float eps, cudaStream_t stream);
+int launch_finalize(float* sums, const __half* scale, const __half* residual, __half* C, int M, int N,
+                    cudaStream_t stream);
+int launch_rmsnorm_finalize(float* sums, const __half* scale, const __half* residual, __half* h_out,
+                            const __half* gamma, __half* xn_out, int M, int n, float eps, cudaStream_t stream);
+int launch_swiglu_finalize(float* gate_sums, const __half* gate_scale, float* up_sums, const __half* up_scale,
+                           __half* act_out, int M, int n, cudaStream_t stream);
 int launch_swiglu(__half* gate_inout, const __half* up, int M, int n, cudaStream_t stream);
 int launch_add_residual(__half* out, const __half* in, size_t count, cudaStream_t stream);
 int launch_qkv_split_store(const __half* qkv, __half* q_out, __half* kcache, __half* vcache, int B, int S, int H,
@@ -48,7 +50,9 @@ int launch_advance_steps(int* steps, int count, int delta, cudaStream_t stream);
 
 // attention.cu
 struct DecodeAttnArgs {
-    const __half* qkv;        // [B][3][H][D] fused projection output of the new token
+    const __half* qkv;        // [B][3][H][D] fused projection output of the new token, or null with:
+    float* qkv_sums;          // [B][3*H*D] fp32 sums of the projection GEMM, finalized (and zeroed) here
+    const __half* qkv_scale;  // [3*H*D] per-channel scales of that projection
     __half* kcache;           // [B_max][H][T_max][D]
     __half* vcache;
     __half* ctx;              // [B][H*D]

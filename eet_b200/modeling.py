@@ -332,7 +332,10 @@ class _CausalLMBase:
 
     # -- greedy generation ------------------------------------------------------------------------------
     def _decode_eager(self, ids, pad):
-        hidden = self.model(input_ids=ids, first_pass=False)
+        # the whole chain of ops below belongs to this library, so every projection's epilogue may run
+        # inside the kernel that consumes it
+        with EET.deferred_epilogue():
+            hidden = self.model(input_ids=ids, first_pass=False)
         return torch.argmax(self.lm_head(hidden)[:, -1, :], dim=-1, keepdim=True)
 
     def _capture(self, B):

@@ -73,9 +73,9 @@ int eet_repack_ref_w8(const void* ref_packed, int K, int N, void* packed, void* 
  * W8A16 GEMM
  * ---------------------------------------------------------------------------------------------- */
 
-/* Scratch needed by eet_gemm_w8a16 for a problem of this size.  The scratch must be zero before its
- * first use (e.g. cudaMemset once after allocation); every call leaves it zero again.  Calls that share
- * one scratch buffer must not overlap on the GPU. */
+/* Scratch needed by eet_gemm_w8a16 for a problem of this size (fp32 sums of up to 128 rows).  The scratch
+ * must be zero before its first use (e.g. cudaMemset once after allocation); every call leaves it zero
+ * again.  Calls that share one scratch buffer must not overlap on the GPU. */
 size_t eet_gemm_w8a16_workspace_bytes(int M, int N, int K);
 
 /*
@@ -93,6 +93,24 @@ size_t eet_gemm_w8a16_workspace_bytes(int M, int N, int K);
 int eet_gemm_w8a16(const void* A, const void* packedB, const void* scale, void* C, int M, int N, int K,
                    const void* residual, int epilogue, void* ws, size_t ws_bytes, void* stream);
 
+/*
+ * The two halves of eet_gemm_w8a16 for small M (the decode regime), exposed so that the second half can be
+ * fused into the kernel that consumes the product.
+ *
+ * eet_gemm_w8a16_accum ADDS sum_k A[m][k] * q[k][n] (q = the int8 weight values, unscaled) into the fp32
+ * buffer sums[M][N]; with packedB2 / sums2 a second weight of the same shape (the FFN "up" projection next
+ * to "gate", csrc/op/gated_ffn_int8.cpp:253-301) is walked by the same launch.  Buffers must be zero on
+ * entry unless accumulation onto earlier sums is wanted.
+ *
+ * eet_gemm_w8a16_finalize turns sums into C = fp16(sums * scale) (+ residual, fp16 add) - the epilogue of
+ * the reference GEMM (cutlass_extensions epilogue_helpers.h:73-80) and its add_input kernel
+ * (csrc/core/add_bias.cu:22-28) - and puts sums back to zero.  eet_rmsnorm_finalize, eet_swiglu_finalize
+ * and eet_decode_mha (qkv_sums) do the same inside the next kernel of a decode step.
+ */
+int eet_gemm_w8a16_accum(const void* A, const void* packedB, float* sums, int M, int N, int K, const void* packedB2,
+                         float* sums2, void* stream);
+int eet_gemm_w8a16_finalize(float* sums, const void* scale, const void* residual, void* C, int M, int N, void* stream);
+
 /* ------------------------------------------------------------------------------------------------
  * Kernels between the GEMMs
  * ---------------------------------------------------------------------------------------------- */
@@ -100,6 +118,21 @@ int eet_gemm_w8a16(const void* A, const void* packedB, const void* scale, void* 
 /* y = x * rsqrt(mean(x^2) + eps) * gamma over rows of length n.
  * Replaces: RMSnorm<half> (csrc/core/layer_norm.cu:580-625 -> T5norm1_kernel_opt :490-531). */
 int eet_rmsnorm(const void* x, const void* gamma, void* y, int M, int n, float eps, void* stream);
+
+/*
+ * Decode-step head of an attention or FFN block: with sums != NULL, first h = fp16(sums * scale) + residual
+ * (finishing the projection GEMM that feeds the block, see eet_gemm_w8a16_finalize) is written to h_out and
+ * sums is zeroed; with sums == NULL, h = residual.  Then xn_out = RMSNorm(h) * gamma.
+ * Replaces: add_input<half> (csrc/core/add_bias.cu:22-28) + RMSnorm<half> (csrc/core/layer_norm.cu:580-625).
+ */
+int eet_rmsnorm_finalize(float* sums, const void* scale, const void* residual, void* h_out, const void* gamma,
+                         void* xn_out, int M, int n, float eps, void* stream);
+
+/* act_out = up * silu(gate) where gate = fp16(gate_sums * gate_scale), up = fp16(up_sums * up_scale) are the
+ * unfinished products of eet_gemm_w8a16_accum; both sum buffers are zeroed.
+ * Replaces: the epilogues of the gate / up GEMMs + gated_silu<half> (csrc/core/activation_kernel.cu:106-124). */
+int eet_swiglu_finalize(float* gate_sums, const void* gate_scale, float* up_sums, const void* up_scale, void* act_out,
+                        int M, int n, void* stream);
 
 /* gate <- up * silu(gate), in place.  Replaces: gated_act_kernel<half> with act_type silu
  * (csrc/core/activation_kernel.cu:275-338 -> gated_silu :106-124). */
@@ -135,6 +168,8 @@ int eet_prefill_mha(const void* q, const void* kcache, const void* vcache, void*
  * One decode step of masked multi-head attention for every (batch, head): rotates the new q,k
  * (rope != 0), appends k,v to the caches at position step-1 and attends over positions
  * [pad_len[b], step).  qkv[B][3][H][D] is the fused projection of the new token; ctx[B][H*D].
+ *   qkv_sums    alternative to qkv (pass qkv = NULL): the fp32 sums [B][3*H*D] left by
+ *               eet_gemm_w8a16_accum, finished here as fp16(sums * qkv_scale) and zeroed
  *   step        history length including the new token, used when step_dev is NULL
  *   step_dev    optional device int32 holding the same number (lets a captured CUDA graph be replayed
  *               while the step advances on the device, see eet_advance_steps)
@@ -146,9 +181,10 @@ int eet_prefill_mha(const void* q, const void* kcache, const void* vcache, void*
  *           fused_masked_attention_dispatch<half> (:1338-1426 -> :1155-1336) and the decode call of
  *           fused_QKV_bias_rotary_kernel (csrc/op/llama_mmha.cpp:241).
  */
-int eet_decode_mha(const void* qkv, void* kcache, void* vcache, void* ctx, int B, int H, int D, int T_max, int step,
-                   const int* step_dev, const int64_t* pad_len, const void* alibi, int alibi_stride,
-                   const float* alibi_slopes, int rope, float rope_base, int splits, void* stream);
+int eet_decode_mha(const void* qkv, float* qkv_sums, const void* qkv_scale, void* kcache, void* vcache, void* ctx,
+                   int B, int H, int D, int T_max, int step, const int* step_dev, const int64_t* pad_len,
+                   const void* alibi, int alibi_stride, const float* alibi_slopes, int rope, float rope_base, int splits,
+                   void* stream);
 
 /* Scratch needed by eet_reorder_kv: 2 * B * H * step * D halves. */
 size_t eet_reorder_kv_workspace_bytes(int B, int H, int D, int step);

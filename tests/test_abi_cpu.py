@@ -20,7 +20,7 @@ def test_header_symbols_are_exported_and_bound():
     for n in names:
         assert hasattr(raw, n), f"{n} is declared in include/eet_b200.h but not exported"
     assert sorted(_lib.SIGNATURES) == names, "ctypes table and header disagree"
-    assert _lib.lib.eet_abi_version() == 1
+    assert _lib.lib.eet_abi_version() == 2
 
 
 def test_argument_validation_happens_before_any_cuda_call():
@@ -31,7 +31,9 @@ def test_argument_validation_happens_before_any_cuda_call():
     assert rc != 0 and b"multiples of 64" in lib.eet_last_error()
     rc = lib.eet_quantize_w8(None, 0, 64, 64, None, None, None, 0, None, 0, None)
     assert rc != 0 and b"NULL" in lib.eet_last_error()
-    rc = lib.eet_decode_mha(None, None, None, None, 1, 1, 128, 8, 1, None, None, None, 0, None, 1, 10000.0, 0, None)
+    rc = lib.eet_decode_mha(None, None, None, None, None, None, 1, 1, 128, 8, 1, None, None, None, 0, None, 1, 10000.0, 0,
+                            None)
     assert rc != 0
-    assert lib.eet_gemm_w8a16_workspace_bytes(16, 4096, 4096) == 16 * 4096 * 4 + 64 * 4 * 4
+    assert lib.eet_gemm_w8a16_workspace_bytes(16, 4096, 4096) == 16 * 4096 * 4
+    assert lib.eet_gemm_w8a16_workspace_bytes(4096, 4096, 4096) == 128 * 4096 * 4
     assert lib.eet_quantize_w8_workspace_bytes(4096, 11008) == 11008 * 4

@@ -19,7 +19,7 @@ def _decode(qkv, kc, vc, step, pad=None, alibi=None, slopes=None, rope=1, splits
     B, _, H, D = qkv.shape
     T = kc.shape[2]
     ctx = torch.empty(B, H * D, dtype=torch.float16, device="cuda")
-    check(lib.eet_decode_mha(qkv.data_ptr(), kc.data_ptr(), vc.data_ptr(), ctx.data_ptr(), B, H, D, T, step,
+    check(lib.eet_decode_mha(qkv.data_ptr(), None, None, kc.data_ptr(), vc.data_ptr(), ctx.data_ptr(), B, H, D, T, step,
                              None if step_dev is None else step_dev.data_ptr(),
                              None if pad is None else pad.data_ptr(),
                              None if alibi is None else alibi.data_ptr(), 0 if alibi is None else alibi.shape[-1],
@@ -139,3 +139,25 @@ def test_prefill(S, mode):
     got = ctx.cpu().view(B, S, H, D).transpose(1, 2)
     # the oracle rounds probabilities to fp16 like the reference's score buffer; this kernel keeps fp32
     assert torch.allclose(got.float(), ref.float(), atol=4e-3, rtol=4e-3)
+
+
+def test_decode_finishes_projection_sums_itself():
+    """qkv given as the fp32 sums of the projection GEMM + per-channel scales: same result as the fp16 form,
+    and the sums are zero afterwards."""
+    from eet_b200._lib import check, lib
+    B, H, D, T, step = 2, 3, 128, 64, 33
+    gen = torch.Generator().manual_seed(12)
+    sums = torch.randn(B, 3 * H * D, generator=gen) * 300
+    scale = (torch.rand(3 * H * D, generator=gen) * 4e-3 + 1e-3).half()
+    qkv = (sums * scale.float()).half().view(B, 3, H, D)
+    kh = torch.randn(B, H, T, D, generator=gen).half()
+    vh = torch.randn(B, H, T, D, generator=gen).half()
+    ref, kc_ref, _ = _oracle_decode(qkv, kh, vh, step, None, None, True)
+    kc, vc, sums_c, scale_c = kh.cuda(), vh.cuda(), sums.cuda(), scale.cuda()
+    ctx = torch.empty(B, H * D, dtype=torch.float16, device="cuda")
+    check(lib.eet_decode_mha(None, sums_c.data_ptr(), scale_c.data_ptr(), kc.data_ptr(), vc.data_ptr(), ctx.data_ptr(),
+                             B, H, D, T, step, None, None, None, 0, None, 1, 10000.0, 4, _stream()))
+    torch.cuda.synchronize()
+    assert _close(ctx.cpu().view(B, H, D), ref)
+    assert _close(kc.cpu()[:, :, step - 1], kc_ref[:, :, step - 1])
+    assert float(sums_c.abs().max()) == 0

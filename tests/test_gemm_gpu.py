@@ -108,3 +108,48 @@ def test_empty_and_invalid():
     assert out.shape == (0, 64)
     rc = _lib.lib.eet_gemm_w8a16(1, 1, 1, 1, 1, 64, 100, None, 0, None, 0, None)
     assert rc != 0
+
+
+def test_accumulate_and_fused_finalize_kernels():
+    """The decode-path split of the GEMM: sums from eet_gemm_w8a16_accum (two weights in one launch), finished
+    by the generic finalize kernel, by the RMSNorm head and by the SwiGLU kernel - each against the oracle."""
+    from eet_b200 import EET
+    from eet_b200._lib import check, lib
+    stream = torch.cuda.current_stream().cuda_stream
+    M, K, N = 8, 512, 1024
+    x, q1, s1 = _case(K, N, M, seed=21)
+    _, q2, s2 = _case(K, N, M, seed=22)
+    xc = x.cuda()
+    p1, p2 = EET.preprocess_weights(q1).cuda(), EET.preprocess_weights(q2).cuda()
+    s1c, s2c = s1.cuda(), s2.cuda()
+    sums1 = torch.zeros(M, N, dtype=torch.float32, device="cuda")
+    sums2 = torch.zeros_like(sums1)
+    EET.gemm_w8a16_accum(xc, p1, sums1, p2, sums2)
+    want1 = x.double() @ q1.double()
+    want2 = x.double() @ q2.double()
+    assert torch.allclose(sums1.cpu().double(), want1, rtol=1e-5, atol=1e-2)
+    assert torch.allclose(sums2.cpu().double(), want2, rtol=1e-5, atol=1e-2)
+    # SwiGLU head: gate = fp16(sums1*s1), up = fp16(sums2*s2)
+    act = torch.empty(M, N, dtype=torch.float16, device="cuda")
+    g_ref, u_ref = (sums1.cpu() * s1.float()).half(), (sums2.cpu() * s2.float()).half()
+    check(lib.eet_swiglu_finalize(sums1.data_ptr(), s1c.data_ptr(), sums2.data_ptr(), s2c.data_ptr(), act.data_ptr(),
+                                  M, N, stream))
+    ref = ops.gated_silu(g_ref, u_ref)
+    assert torch.allclose(act.cpu().float(), ref.float(), rtol=2e-3, atol=1e-5)
+    assert float(sums1.abs().max()) == 0 and float(sums2.abs().max()) == 0
+    # RMSNorm head: h = fp16(sums*s) + residual, xn = rmsnorm(h)
+    EET.gemm_w8a16_accum(xc, p1, sums1)
+    res = torch.randn(M, N).half()
+    gamma = (1 + 0.1 * torch.randn(N)).half()
+    h_out = torch.empty(M, N, dtype=torch.float16, device="cuda")
+    xn = torch.empty_like(h_out)
+    resc, gc = res.cuda(), gamma.cuda()
+    h_ref = ops.add_residual((sums1.cpu() * s1.float()).half(), res)
+    check(lib.eet_rmsnorm_finalize(sums1.data_ptr(), s1c.data_ptr(), resc.data_ptr(), h_out.data_ptr(), gc.data_ptr(),
+                                   xn.data_ptr(), M, N, 1e-6, stream))
+    assert torch.equal(h_out.cpu(), h_ref)
+    assert torch.allclose(xn.cpu().float(), ops.rmsnorm(h_ref, gamma, 1e-6).float(), rtol=1e-3, atol=1e-3)
+    assert float(sums1.abs().max()) == 0
+    # without sums it is a plain RMSNorm of `residual`
+    check(lib.eet_rmsnorm_finalize(None, None, resc.data_ptr(), None, gc.data_ptr(), xn.data_ptr(), M, N, 1e-6, stream))
+    assert torch.allclose(xn.cpu().float(), ops.rmsnorm(res, gamma, 1e-6).float(), rtol=1e-3, atol=1e-3)
