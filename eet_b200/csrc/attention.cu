@@ -27,8 +27,14 @@ namespace eet {
 
 namespace {
 
-constexpr int kAttnThreads = 256;
-constexpr int kHalfWarps = kAttnThreads / 16;
+constexpr int kAttnConsumerWarps = 4;
+constexpr int kAttnConsumerThreads = kAttnConsumerWarps * 32;
+constexpr int kAttnThreads = kAttnConsumerThreads + 32;  // + one producer warp
+constexpr int kHalfWarps = kAttnConsumerThreads / 16;
+constexpr int kAttnTile = 32;                             // time steps per shared-memory stage
+constexpr int kAttnStages = 2;
+constexpr int kAttnRowBytes = 256;                        // D = 128 halves
+constexpr int kAttnStageBytes = 2 * kAttnTile * kAttnRowBytes;  // K tile + V tile
 
 struct OnlineState {
     float m;       // running max
@@ -75,28 +81,48 @@ __device__ __forceinline__ void online_update(OnlineState& st, float s, const ui
     st.m = m_new;
 }
 
+struct AttnSmem {
+    uint64_t full[kAttnStages];
+    uint64_t empty[kAttnStages];
+    __half q[128], k[128], v[128];
+    float m[kHalfWarps], l[kHalfWarps];
+    float acc[kHalfWarps][128];
+    float c_acc[128];  // this CTA's merged partial, read by cluster rank 0 through distributed shared memory
+    float c_ml[2];
+    volatile int abort;
+};
+
 // D is fixed at 128 (16 lanes x 8 halves); the dispatch rejects other head sizes.
-__global__ void __launch_bounds__(kAttnThreads)
+//
+// Data path: the history slice of a CTA is contiguous in the [B][H][T][D] caches, so a producer warp
+// streams it with 1-D bulk copies (TMA engine) of 32 time steps of K and of V per stage into a two-stage
+// ring; five CTAs per SM keep ~160 KiB in flight.  Register-level loads of the same bytes stall on the
+// number of outstanding L1 misses long before HBM is busy.  Four consumer warps take a half-warp per time
+// step from shared memory.
+__global__ void __launch_bounds__(kAttnThreads, 5)
 decode_mha_kernel(DecodeAttnArgs a)
 {
     constexpr int D = 128;
+    extern __shared__ __align__(128) uint8_t attn_dyn[];
+    __shared__ __align__(16) AttnSmem sm;
     cg::cluster_group cluster = cg::this_cluster();
     const int splits = (int)cluster.num_blocks();
     const int split = (int)cluster.block_rank();
     const int bh = blockIdx.y;
     const int b = bh / a.H, h = bh % a.H;
     const int tid = threadIdx.x;
-    const int hw = tid >> 4;  // half-warp index inside the CTA
+    const int warp = tid >> 5;
+    const int hw = tid >> 4;  // half-warp index inside the CTA (consumers: 0..7)
     const int hl = tid & 15;  // lane inside the half-warp: owns dims 8*hl .. 8*hl+7
 
-    __shared__ __align__(16) __half s_q[D];
-    __shared__ __align__(16) __half s_k[D];
-    __shared__ __align__(16) __half s_v[D];
-    __shared__ float s_m[kHalfWarps], s_l[kHalfWarps];
-    __shared__ __align__(16) float s_acc[kHalfWarps][D];
-    // this CTA's merged partial, read by cluster rank 0 through distributed shared memory
-    __shared__ __align__(16) float c_acc[D];
-    __shared__ float c_ml[2];
+    if (tid == 0) {
+        for (int s = 0; s < kAttnStages; ++s) {
+            mbar_init(&sm.full[s], 1);
+            mbar_init(&sm.empty[s], kAttnConsumerWarps);
+        }
+        sm.abort = 0;
+        mbar_fence_init();
+    }
 
     // everything this kernel reads that an earlier kernel of the same step produced (the projection of the
     // new token, the device-resident step) comes after this wait
@@ -105,144 +131,215 @@ decode_mha_kernel(DecodeAttnArgs a)
     const int step = a.step_dev ? *a.step_dev : a.step;
     const size_t inner = (size_t)a.H * D;
 
-    // ---- new token: rotate q,k at position step-1, round to fp16 as the reference's buffers do ----
-    // The projection arrives either as fp16 [B][3][H][D] or as the fp32 sums of the skinny GEMM, which are
-    // finished here: fp16(sum * scale), the value the reference's GEMM epilogue would have stored.
-    auto proj = [&](int which, int i) -> __half {
-        const size_t col = (size_t)which * inner + (size_t)h * D + i;
-        if (a.qkv_sums != nullptr) {
-            return __float2half(__ldcg(a.qkv_sums + (size_t)b * 3 * inner + col) * __half2float(a.qkv_scale[col]));
-        }
-        return a.qkv[(size_t)b * 3 * inner + col];
-    };
-    if (tid < D / 2) {
-        const int i = tid;
-        const __half hq1 = proj(0, i), hq2 = proj(0, i + D / 2), hk1 = proj(1, i), hk2 = proj(1, i + D / 2);
-        if (a.rope) {
-            const float q1 = __half2float(hq1), q2 = __half2float(hq2), k1 = __half2float(hk1), k2 = __half2float(hk2);
-            const float ang = (float)(step - 1) / powf(a.rope_base, (float)(2 * i) / (float)D);
-            const float c = cosf(ang), sn = sinf(ang);
-            s_q[i] = __float2half(q1 * c - q2 * sn);
-            s_q[i + D / 2] = __float2half(q2 * c + q1 * sn);
-            s_k[i] = __float2half(k1 * c - k2 * sn);
-            s_k[i + D / 2] = __float2half(k2 * c + k1 * sn);
-        }
-        else {
-            s_q[i] = hq1;
-            s_q[i + D / 2] = hq2;
-            s_k[i] = hk1;
-            s_k[i + D / 2] = hk2;
-        }
-    }
-    else if (tid < D) {
-        const int i = tid - D / 2;
-        s_v[i] = proj(2, i);
-        s_v[i + D / 2] = proj(2, i + D / 2);
-    }
-    __syncthreads();
-
-    const size_t cache_row0 = ((size_t)b * a.H + h) * a.T_max;
-    const uint4* kc = reinterpret_cast<const uint4*>(a.kcache + cache_row0 * D);
-    const uint4* vc = reinterpret_cast<const uint4*>(a.vcache + cache_row0 * D);
-
     // ---- slice of the history owned by this CTA ----
-    const int chunk = (((step + splits - 1) / splits) + kHalfWarps - 1) / kHalfWarps * kHalfWarps;
+    const int chunk = (((step + splits - 1) / splits) + kAttnTile - 1) / kAttnTile * kAttnTile;
     const int t_begin = split * chunk;
     const int t_end = min(step, t_begin + chunk);
     int pad = 0;
     if (a.pad_len != nullptr) pad = (int)a.pad_len[b];
+    const int t_first = max(t_begin, pad / kAttnTile * kAttnTile);  // whole tiles left of the padding are skipped
+    const int n_tiles = (t_end > t_first) ? (t_end - t_first + kAttnTile - 1) / kAttnTile : 0;
+    const size_t cache_row0 = ((size_t)b * a.H + h) * a.T_max;
+    __syncthreads();  // barriers initialised
 
-    // cache append: done by the CTA whose slice holds the newest position
-    if (step - 1 >= t_begin && step - 1 < t_end && tid < 32) {
-        uint4* kd = reinterpret_cast<uint4*>(a.kcache + (cache_row0 + step - 1) * D);
-        uint4* vd = reinterpret_cast<uint4*>(a.vcache + (cache_row0 + step - 1) * D);
-        if (tid < 16) {
-            kd[tid] = reinterpret_cast<const uint4*>(s_k)[tid];
-        }
-        else {
-            vd[tid - 16] = reinterpret_cast<const uint4*>(s_v)[tid - 16];
-        }
-    }
-
-    float q[8];
-    {
-        const uint4 qv = reinterpret_cast<const uint4*>(s_q)[hl];
-        const __half2* qh = reinterpret_cast<const __half2*>(&qv);
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            const float2 f = __half22float2(qh[e]);
-            q[2 * e] = f.x;
-            q[2 * e + 1] = f.y;
-        }
-    }
-    // the reference multiplies by the fp16-rounded 1/sqrt(D) (csrc/op/llama_mmha.cpp:80-84)
-    const float scalar = __half2float(__float2half(sqrtf(1.0f / D)));
-    const float slope = a.alibi_slopes ? a.alibi_slopes[h] : 0.f;
-
-    OnlineState st;
-    st.m = -1e20f;
-    st.l = 0.f;
-#pragma unroll
-    for (int e = 0; e < 8; ++e) st.acc[e] = 0.f;
-
-    constexpr int U = 4;  // time steps in flight per half-warp
-    for (int t0 = max(t_begin, pad / kHalfWarps * kHalfWarps) + hw; t0 < t_end; t0 += kHalfWarps * U) {
-        uint4 kv[U], vv[U];
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-            const int t = t0 + u * kHalfWarps;
-            if (t < t_end && t >= pad) {
-                if (t == step - 1) {
-                    kv[u] = reinterpret_cast<const uint4*>(s_k)[hl];
-                    vv[u] = reinterpret_cast<const uint4*>(s_v)[hl];
+    if (warp == kAttnConsumerWarps) {
+        // ------------------------------------------------------------------ producer warp (one lane)
+        if ((tid & 31) == 0) {
+            for (int j = 0; j < n_tiles; ++j) {
+                const int s = j % kAttnStages;
+                if (j >= kAttnStages && !sm.abort) {
+                    if (!mbar_wait_bounded(&sm.empty[s], ((j / kAttnStages) - 1) & 1)) {
+                        sm.abort = 1;
+                        g_device_status = 3;
+                    }
                 }
-                else {
-                    kv[u] = __ldg(kc + (size_t)t * (D / 8) + hl);
-                    vv[u] = __ldg(vc + (size_t)t * (D / 8) + hl);
-                }
+                const int t = t_first + j * kAttnTile;
+                // rows up to the cache end may be copied: rows at or beyond `step` are never used
+                const int rows = min(kAttnTile, a.T_max - t);
+                uint8_t* dst = attn_dyn + (size_t)s * kAttnStageBytes;
+                mbar_arrive_expect_tx(&sm.full[s], (uint32_t)(2 * rows * kAttnRowBytes));
+                bulk_g2s(dst, a.kcache + (cache_row0 + t) * D, (uint32_t)(rows * kAttnRowBytes), &sm.full[s]);
+                bulk_g2s(dst + kAttnTile * kAttnRowBytes, a.vcache + (cache_row0 + t) * D,
+                         (uint32_t)(rows * kAttnRowBytes), &sm.full[s]);
             }
         }
+    }
+    else {
+        // ---- new token: rotate q,k at position step-1, round to fp16 as the reference's buffers do ----
+        // The projection arrives either as fp16 [B][3][H][D] or as the fp32 sums of the skinny GEMM, which
+        // are finished here: fp16(sum * scale), the value the reference's GEMM epilogue would have stored.
+        auto proj = [&](int which, int i) -> __half {
+            const size_t col = (size_t)which * inner + (size_t)h * D + i;
+            if (a.qkv_sums != nullptr) {
+                return __float2half(__ldcg(a.qkv_sums + (size_t)b * 3 * inner + col) * __half2float(a.qkv_scale[col]));
+            }
+            return a.qkv[(size_t)b * 3 * inner + col];
+        };
+        if (tid < D / 2) {
+            const int i = tid;
+            const __half hq1 = proj(0, i), hq2 = proj(0, i + D / 2), hk1 = proj(1, i), hk2 = proj(1, i + D / 2);
+            if (a.rope) {
+                const float q1 = __half2float(hq1), q2 = __half2float(hq2);
+                const float k1 = __half2float(hk1), k2 = __half2float(hk2);
+                const float ang = (float)(step - 1) / powf(a.rope_base, (float)(2 * i) / (float)D);
+                const float c = cosf(ang), sn = sinf(ang);
+                sm.q[i] = __float2half(q1 * c - q2 * sn);
+                sm.q[i + D / 2] = __float2half(q2 * c + q1 * sn);
+                sm.k[i] = __float2half(k1 * c - k2 * sn);
+                sm.k[i + D / 2] = __float2half(k2 * c + k1 * sn);
+            }
+            else {
+                sm.q[i] = hq1;
+                sm.q[i + D / 2] = hq2;
+                sm.k[i] = hk1;
+                sm.k[i + D / 2] = hk2;
+            }
+        }
+        else {
+            const int i = tid - D / 2;
+            sm.v[i] = proj(2, i);
+            sm.v[i + D / 2] = proj(2, i + D / 2);
+        }
+        asm volatile("bar.sync 1, %0;" ::"n"(kAttnConsumerThreads) : "memory");
+
+        // cache append: done by the CTA whose slice holds the newest position
+        if (step - 1 >= t_begin && step - 1 < t_end && tid < 32) {
+            uint4* kd = reinterpret_cast<uint4*>(a.kcache + (cache_row0 + step - 1) * D);
+            uint4* vd = reinterpret_cast<uint4*>(a.vcache + (cache_row0 + step - 1) * D);
+            if (tid < 16) {
+                kd[tid] = reinterpret_cast<const uint4*>(sm.k)[tid];
+            }
+            else {
+                vd[tid - 16] = reinterpret_cast<const uint4*>(sm.v)[tid - 16];
+            }
+        }
+
+        float q[8];
+        {
+            const uint4 qv = reinterpret_cast<const uint4*>(sm.q)[hl];
+            const __half2* qh = reinterpret_cast<const __half2*>(&qv);
 #pragma unroll
-        for (int u = 0; u < U; ++u) {
-            const int t = t0 + u * kHalfWarps;
-            // every lane of the half-warp takes the same branch: t does not depend on hl
-            if (t < t_end && t >= pad) {
-                float s = half_warp_sum(dot8(kv[u], q)) * scalar;
-                __half sh = __float2half(s);
+            for (int e = 0; e < 4; ++e) {
+                const float2 f = __half22float2(qh[e]);
+                q[2 * e] = f.x;
+                q[2 * e + 1] = f.y;
+            }
+        }
+        // the reference multiplies by the fp16-rounded 1/sqrt(D) (csrc/op/llama_mmha.cpp:80-84)
+        const float scalar = __half2float(__float2half(sqrtf(1.0f / D)));
+        const float slope = a.alibi_slopes ? a.alibi_slopes[h] : 0.f;
+
+        OnlineState st;
+        st.m = -1e20f;
+        st.l = 0.f;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) st.acc[e] = 0.f;
+
+        constexpr int U = kAttnTile / kHalfWarps;  // time steps per half-warp and tile
+        for (int j = 0; j < n_tiles; ++j) {
+            const int s = j % kAttnStages;
+            if (!sm.abort) {
+                if (!mbar_wait_bounded(&sm.full[s], (j / kAttnStages) & 1)) {
+                    sm.abort = 1;
+                    g_device_status = 3;
+                }
+            }
+            const uint4* kt = reinterpret_cast<const uint4*>(attn_dyn + (size_t)s * kAttnStageBytes);
+            const uint4* vt = kt + kAttnTile * (kAttnRowBytes / 16);
+            const int t0 = t_first + j * kAttnTile;
+            uint4 kv[U], vv[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int r = hw + u * kHalfWarps;
+                const int t = t0 + r;
+                if (t == step - 1) {  // the newest row is not in the cache copy: take it from the projection
+                    kv[u] = reinterpret_cast<const uint4*>(sm.k)[hl];
+                    vv[u] = reinterpret_cast<const uint4*>(sm.v)[hl];
+                }
+                else {
+                    kv[u] = kt[r * (kAttnRowBytes / 16) + hl];
+                    vv[u] = vt[r * (kAttnRowBytes / 16) + hl];
+                }
+            }
+            // the tile's bytes are in registers: hand the stage back to the producer
+            __syncwarp();
+            if ((tid & 31) == 0) mbar_arrive(&sm.empty[s]);
+            // the U time steps of this half-warp are folded into the running softmax together: independent
+            // dot products and shuffle chains, one rescale of the accumulators per tile
+            float sc[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) sc[u] = dot8(kv[u], q);
+            const uint32_t hmask = 0xffffu << (tid & 16);
+#pragma unroll
+            for (int o = 8; o > 0; o >>= 1) {
+#pragma unroll
+                for (int u = 0; u < U; ++u) sc[u] += __shfl_xor_sync(hmask, sc[u], o);
+            }
+            float m_new = st.m;
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int t = t0 + hw + u * kHalfWarps;
+                __half sh = __float2half(sc[u] * scalar);
                 if (a.alibi != nullptr) {
-                    sh = __hadd(sh, a.alibi[(size_t)h * a.alibi_stride + t]);
+                    sh = __hadd(sh, a.alibi[(size_t)h * a.alibi_stride + min(t, step - 1)]);
                 }
                 else if (a.alibi_slopes != nullptr) {
                     sh = __hadd(sh, __float2half_rn(slope * (float)t));
                 }
-                online_update(st, __half2float(sh), vv[u]);
+                // positions outside [pad, t_end) get -inf, i.e. probability 0 (m_new stays >= -1e20)
+                const bool valid = (t < t_end && t >= pad);
+                sc[u] = valid ? __half2float(sh) : -INFINITY;
+                if (!valid) vv[u] = make_uint4(0, 0, 0, 0);  // rows past the history may hold anything, even NaN
+                m_new = fmaxf(m_new, sc[u]);
+            }
+            const float corr = __expf(st.m - m_new);
+            float p[U];
+            float psum = 0.f;
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                p[u] = __expf(sc[u] - m_new);
+                psum += p[u];
+            }
+            st.l = st.l * corr + psum;
+            st.m = m_new;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                float a0 = st.acc[2 * e] * corr, a1 = st.acc[2 * e + 1] * corr;
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    const float2 f = __half22float2(reinterpret_cast<const __half2*>(&vv[u])[e]);
+                    a0 += p[u] * f.x;
+                    a1 += p[u] * f.y;
+                }
+                st.acc[2 * e] = a0;
+                st.acc[2 * e + 1] = a1;
             }
         }
-    }
 
-    // ---- merge the half-warps of this CTA ----
-    if (hl == 0) {
-        s_m[hw] = st.m;
-        s_l[hw] = st.l;
-    }
-#pragma unroll
-    for (int e = 0; e < 8; ++e) s_acc[hw][hl * 8 + e] = st.acc[e];
-    __syncthreads();
-    if (tid < D) {
-        float m = -1e20f;
-#pragma unroll
-        for (int w = 0; w < kHalfWarps; ++w) m = fmaxf(m, s_m[w]);
-        float l = 0.f, acc = 0.f;
-#pragma unroll
-        for (int w = 0; w < kHalfWarps; ++w) {
-            const float c = __expf(s_m[w] - m);
-            l += s_l[w] * c;
-            acc += s_acc[w][tid] * c;
+        // ---- merge the half-warps of this CTA ----
+        if (hl == 0) {
+            sm.m[hw] = st.m;
+            sm.l[hw] = st.l;
         }
-        c_acc[tid] = acc;
-        if (tid == 0) {
-            c_ml[0] = m;
-            c_ml[1] = l;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) sm.acc[hw][hl * 8 + e] = st.acc[e];
+        asm volatile("bar.sync 1, %0;" ::"n"(kAttnConsumerThreads) : "memory");
+        if (tid < D) {
+            float m = -1e20f;
+#pragma unroll
+            for (int w = 0; w < kHalfWarps; ++w) m = fmaxf(m, sm.m[w]);
+            float l = 0.f, acc = 0.f;
+#pragma unroll
+            for (int w = 0; w < kHalfWarps; ++w) {
+                const float c = __expf(sm.m[w] - m);
+                l += sm.l[w] * c;
+                acc += sm.acc[w][tid] * c;
+            }
+            sm.c_acc[tid] = acc;
+            if (tid == 0) {
+                sm.c_ml[0] = m;
+                sm.c_ml[1] = l;
+            }
         }
     }
 
@@ -257,13 +354,13 @@ decode_mha_kernel(DecodeAttnArgs a)
     if (split == 0 && tid < D) {
         float m = -1e20f;
         for (int r = 0; r < splits; ++r) {
-            const float* rml = cluster.map_shared_rank(c_ml, r);
+            const float* rml = cluster.map_shared_rank(sm.c_ml, r);
             m = fmaxf(m, rml[0]);
         }
         float l = 0.f, acc = 0.f;
         for (int r = 0; r < splits; ++r) {
-            const float* rml = cluster.map_shared_rank(c_ml, r);
-            const float* racc = cluster.map_shared_rank(c_acc, r);
+            const float* rml = cluster.map_shared_rank(sm.c_ml, r);
+            const float* racc = cluster.map_shared_rank(sm.c_acc, r);
             const float c = __expf(rml[0] - m);
             l += rml[1] * c;
             acc += racc[tid] * c;
@@ -383,17 +480,17 @@ int launch_decode_mha(const DecodeAttnArgs& a, cudaStream_t stream)
     if (a.B == 0) return 0;
     int splits = a.splits;
     if (splits == 0) {
-        // enough CTAs for two waves of the machine, but at least 64 time steps per CTA
+        // as many CTAs as fit on the machine at once (5 per SM); at least 64 time steps per CTA
         const int len = a.step_dev ? a.T_max : a.step;
-        const int want = (2 * sm_count() + a.B * a.H - 1) / (a.B * a.H);
+        const int room = 5 * sm_count() / (a.B * a.H);
         splits = 1;
-        while (splits < 8 && splits < want && len / (splits * 2) >= 64) splits *= 2;
+        while (splits < 8 && splits * 2 <= room && len / (splits * 2) >= 64) splits *= 2;
     }
     EET_CHECK(splits == 1 || splits == 2 || splits == 4 || splits == 8, "decode attention: splits must be 1,2,4,8");
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(splits, a.B * a.H, 1);
     cfg.blockDim = dim3(kAttnThreads, 1, 1);
-    cfg.dynamicSmemBytes = 0;
+    cfg.dynamicSmemBytes = kAttnStages * kAttnStageBytes;
     cfg.stream = stream;
     cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
