@@ -46,6 +46,7 @@ static inline bool aligned16(const void* p)
 
 #include "attention.cu"
 #include "gemm_skinny.cu"
+#include "gemm_tc.cu"
 #include "glue.cu"
 #include "quantize.cu"
 
@@ -181,10 +182,15 @@ int eet_gemm_w8a16(const void* A, const void* packedB, const void* scale, void* 
     EET_CHECK(scale && C && aligned16(C) && aligned16(scale), "eet_gemm_w8a16: scale and C must be 16-byte aligned buffers");
     EET_CHECK(epilogue == 0 || epilogue == 1, "eet_gemm_w8a16: unknown epilogue %d", epilogue);
     EET_CHECK(epilogue != 1 || residual != nullptr, "eet_gemm_w8a16: epilogue 1 needs a residual");
+    const __half* res = epilogue == 1 ? (const __half*)residual : nullptr;
+    if (gemm_tc_supported(M, N, K)) {
+        // prefill regime: tcgen05 tensor-core kernel, epilogue fused, no scratch
+        return launch_gemm_tc((const __half*)A, (const uint8_t*)packedB, (const __half*)scale, (__half*)C, res, M, N, K,
+                              (cudaStream_t)stream);
+    }
     EET_CHECK(ws && aligned16(ws) && ws_bytes >= eet_gemm_w8a16_workspace_bytes(M, N, K),
               "eet_gemm_w8a16: workspace of %zu bytes is smaller than the %zu needed", ws_bytes,
               eet_gemm_w8a16_workspace_bytes(M, N, K));
-    const __half* res = epilogue == 1 ? (const __half*)residual : nullptr;
     for (int r0 = 0; r0 < M; r0 += kSkinnyGroupRows) {
         const int rows = (M - r0 < kSkinnyGroupRows) ? (M - r0) : kSkinnyGroupRows;
         GemmArgs a = {};

@@ -1,0 +1,329 @@
+// W8A16 tensor-core GEMM for the prefill regime (M > 16): C[M,N] = A[M,K] (fp16) x dequant(B), B in the
+// W8T64 layout, per-channel fp16 scale (and optional fp16 residual) in the epilogue.
+//
+// Replaces the reference's fpA_intB GEMM (kernel cutlass_extensions/.../gemm/kernel/fpA_intB_gemm.h:60-486,
+// mainloop .../threadblock/dq_mma_multistage.h:490-583: mma.sync m16n8k16 with int8 -> fp16 conversion in
+// registers after ldmatrix), which has no path for sm_90 or later.
+//
+// B200 design (tcgen05 / TMEM, one CTA per 128-channel x BN-token output tile):
+//  * "swap AB": the weights are the 128-row M operand of tcgen05.mma, the tokens the N operand (BN up to
+//    256), so any batch of tokens fills the tensor core and the per-channel scale is per TMEM lane.
+//  * warp 0 (one lane) is the TMA producer: per 64-wide k-block it requests the two 4 KiB W8T64 tiles of
+//    the 128 channels with 1-D bulk copies and the BN x 64 activation tile with one 2-D tensor-map copy
+//    that lands in the 128-byte-swizzled K-major layout the MMA reads.
+//  * warps 2-5 turn each int8 weight tile into fp16 (prmt + sub.f16x2, exact) and write it into shared
+//    memory in the same swizzled K-major layout - the int8 bytes never go through the tensor core as int8
+//    and the weights are never materialised as fp16 in global memory.
+//  * warp 1 (one lane) issues four tcgen05.mma (M128 x BN x K16, fp16 in, fp32 accumulate in TMEM) per
+//    k-block and commits them to the stage's "empty" mbarrier, which releases the stage to the producer.
+//  * after the last k-block warps 2-5 read the accumulator with tcgen05.ld (lane = channel), multiply by
+//    the channel's scale, round once to fp16, add the residual if asked and store.
+//  Three-stage ring of {8 KiB int8 weights, 16 KiB fp16 weights, BN x 128 B activations}.
+//  Every wait is bounded; a wait that runs out sets the device status word, and the CTA still frees its
+//  tensor memory before it returns.
+//
+// Numerics: exact integer weights as fp16, fp32 accumulation, one multiply by the fp16 scale, one rounding
+// to fp16 - the same as the skinny kernel's finalize step.
+#include <cuda.h>
+
+#include "common.cuh"
+#include "kernels.h"
+
+namespace eet {
+
+namespace {
+
+constexpr int kTcThreads = 192;     // warp 0 producer, warp 1 MMA issuer + TMEM owner, warps 2-5 transform/epilogue
+constexpr int kTcStages = 3;
+constexpr int kTcW8Bytes = 2 * kTileBytes;          // 128 channels x 64 k, int8
+constexpr int kTcWhBytes = 128 * 128;               // 128 channels x 64 k, fp16, 128 B per row
+constexpr uint32_t kTcSpin = 1u << 24;
+
+__host__ __device__ constexpr int tc_stage_bytes(int bn)
+{
+    return kTcW8Bytes + kTcWhBytes + bn * 128;
+}
+
+struct TcSmem {
+    uint64_t full[kTcStages];    // TMA bytes of a stage have landed (int8 weights + activations)
+    uint64_t ready[kTcStages];   // fp16 weights of a stage are written (4 transform warps)
+    uint64_t empty[kTcStages];   // the MMAs that read a stage have completed (tcgen05.commit)
+    uint64_t accum;              // all MMAs of the tile have completed
+    uint32_t tmem_base;
+    volatile int abort;
+};
+
+__device__ __forceinline__ bool tc_wait(uint64_t* bar, uint32_t parity, volatile int* abort)
+{
+    if (*abort) return false;
+    for (uint32_t i = 0; i < kTcSpin; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (*abort) return false;
+    }
+    *abort = 1;
+    g_device_status = 2;
+    return false;
+}
+
+// shared-memory matrix descriptor: K-major, 128-byte swizzle, rows of 128 bytes, 8-row groups 1024 B apart
+__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr)
+{
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);        // start address, 16-byte units
+    d |= (uint64_t)1 << 16;                             // leading byte offset (unused with swizzle)
+    d |= (uint64_t)(1024 >> 4) << 32;                   // stride byte offset between 8-row groups
+    d |= (uint64_t)1 << 46;                             // descriptor version of this architecture
+    d |= (uint64_t)2 << 61;                             // SWIZZLE_128B
+    return d;
+}
+
+// instruction descriptor for kind::f16: fp16 A and B, fp32 accumulate, both operands K-major
+__host__ __device__ constexpr uint32_t umma_idesc_f16(int m, int n)
+{
+    return (1u << 4) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, bool accumulate)
+{
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
+        "}\n" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"((uint32_t)accumulate)
+        : "memory");
+}
+
+__device__ __forceinline__ void umma_commit(uint64_t* bar)
+{
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+                 : "memory");
+}
+
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+            smem_u32(smem_dst)),
+        "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32])
+{
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+          "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+          "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+template<int BN>
+__global__ void __launch_bounds__(kTcThreads, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t* __restrict__ Bw, const __half* __restrict__ scale,
+               __half* __restrict__ C, const __half* __restrict__ residual, int M, int N, int K)
+{
+    extern __shared__ __align__(1024) uint8_t tc_dyn[];
+    __shared__ TcSmem sm;
+    // the ring must start on a 1024-byte boundary for the swizzled tiles
+    uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(tc_dyn) + 1023) & ~(uintptr_t)1023);
+    constexpr int kStageBytes = tc_stage_bytes(BN);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n0 = blockIdx.x * 128;   // first output channel of the tile
+    const int m0 = blockIdx.y * BN;    // first token of the tile
+    const int KT = K / kTile;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kTcStages; ++s) {
+            mbar_init(&sm.full[s], 1);
+            mbar_init(&sm.ready[s], 4);
+            mbar_init(&sm.empty[s], 1);
+        }
+        mbar_init(&sm.accum, 1);
+        sm.abort = 0;
+        mbar_fence_init();
+    }
+    if (warp == 1) {
+        // tensor memory: BN fp32 columns x 128 lanes for the accumulator
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)),
+                     "r"((uint32_t)BN)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = sm.tmem_base;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            for (int kb = 0; kb < KT; ++kb) {
+                const int s = kb % kTcStages;
+                if (kb >= kTcStages && !tc_wait(&sm.empty[s], ((kb / kTcStages) - 1) & 1, &sm.abort)) break;
+                uint8_t* st = ring + (size_t)s * kStageBytes;
+                mbar_arrive_expect_tx(&sm.full[s], (uint32_t)(kTcW8Bytes + BN * 128));
+                const uint8_t* w0 = Bw + ((size_t)(n0 / kTile) * KT + kb) * kTileBytes;
+                bulk_g2s(st, w0, kTileBytes, &sm.full[s]);
+                bulk_g2s(st + kTileBytes, w0 + (size_t)KT * kTileBytes, kTileBytes, &sm.full[s]);
+                tma_load_2d(st + kTcW8Bytes + kTcWhBytes, &tmap_x, kb * kTile, m0, &sm.full[s]);
+            }
+        }
+    }
+    else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_idesc_f16(128, BN);
+            for (int kb = 0; kb < KT; ++kb) {
+                const int s = kb % kTcStages;
+                const uint32_t ph = (kb / kTcStages) & 1;
+                if (!tc_wait(&sm.full[s], ph, &sm.abort)) break;    // activations landed
+                if (!tc_wait(&sm.ready[s], ph, &sm.abort)) break;   // fp16 weights written
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint8_t* st = ring + (size_t)s * kStageBytes;
+                const uint64_t a_desc = umma_desc_sw128(smem_u32(st + kTcW8Bytes));
+                const uint64_t b_desc = umma_desc_sw128(smem_u32(st + kTcW8Bytes + kTcWhBytes));
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    // 16 reduction indices = 32 bytes along the swizzled row: +2 in 16-byte address units
+                    umma_f16(tmem, a_desc + (uint64_t)(2 * k), b_desc + (uint64_t)(2 * k), idesc, (kb | k) != 0);
+                }
+                umma_commit(&sm.empty[s]);
+            }
+            umma_commit(&sm.accum);
+        }
+    }
+    else {
+        // ------------------------------------------------------------------ transform warps, then epilogue
+        const int tw = threadIdx.x - 64;          // 0..127
+        for (int kb = 0; kb < KT; ++kb) {
+            const int s = kb % kTcStages;
+            const uint32_t ph = (kb / kTcStages) & 1;
+            if (!tc_wait(&sm.full[s], ph, &sm.abort)) break;
+            uint8_t* st = ring + (size_t)s * kStageBytes;
+            const uint8_t* w8 = st;
+            uint8_t* wh = st + kTcW8Bytes;
+#pragma unroll
+            for (int pass = 0; pass < 4; ++pass) {
+                const int r = pass * 32 + (tw >> 2);   // channel row of the tile, 0..127
+                const int qd = tw & 3;                 // 16-byte quarter of its 64 int8 values
+                const uint4 raw = *reinterpret_cast<const uint4*>(w8 + r * 64 + qd * 16);
+                uint4 o0, o1;
+                cvt_u8x4_to_f16x4(raw.x, o0.x, o0.y);
+                cvt_u8x4_to_f16x4(raw.y, o0.z, o0.w);
+                cvt_u8x4_to_f16x4(raw.z, o1.x, o1.y);
+                cvt_u8x4_to_f16x4(raw.w, o1.z, o1.w);
+                uint8_t* row = wh + r * 128;
+                *reinterpret_cast<uint4*>(row + (((2 * qd) ^ (r & 7)) << 4)) = o0;
+                *reinterpret_cast<uint4*>(row + (((2 * qd + 1) ^ (r & 7)) << 4)) = o1;
+            }
+            // make the generic-proxy writes visible to the tensor core (async proxy), then signal
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sm.ready[s]);
+        }
+
+        // ---- epilogue: TMEM lane = channel, columns = tokens ----
+        if (tc_wait(&sm.accum, 0, &sm.abort)) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const int lane_base = (warp & 3) * 32;        // the TMEM lanes this warp may read
+            const int n = n0 + lane_base + lane;
+            const float sc = __half2float(scale[n]);
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                if (m0 + c0 >= M) break;
+                uint32_t v[32];
+                tmem_ld32(tmem + ((uint32_t)lane_base << 16) + (uint32_t)c0, v);
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    const int m = m0 + c0 + j;
+                    if (m < M) {
+                        const size_t o = (size_t)m * N + n;
+                        __half r = __float2half(__uint_as_float(v[j]) * sc);
+                        if (residual != nullptr) r = __hadd(r, residual[o]);
+                        C[o] = r;
+                    }
+                }
+            }
+        }
+    }
+
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)BN) : "memory");
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn()
+{
+    static EncodeTiledFn fn = nullptr;
+    if (fn == nullptr) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess) {
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+        }
+    }
+    return fn;
+}
+
+template<int BN>
+int launch_tc(const CUtensorMap& map, const uint8_t* B, const __half* scale, __half* C, const __half* residual, int M,
+              int N, int K, cudaStream_t stream)
+{
+    static bool attr_set[64] = {};
+    int dev = 0;
+    EET_CUDA(cudaGetDevice(&dev));
+    dev &= 63;
+    const size_t smem = (size_t)kTcStages * tc_stage_bytes(BN) + 1024;
+    if (!attr_set[dev]) {
+        EET_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        attr_set[dev] = true;
+    }
+    dim3 grid(N / 128, (M + BN - 1) / BN);
+    gemm_tc_kernel<BN><<<grid, kTcThreads, smem, stream>>>(map, B, scale, C, residual, M, N, K);
+    EET_LAUNCH_CHECK();
+    return 0;
+}
+
+}  // namespace
+
+bool gemm_tc_supported(int M, int N, int K)
+{
+    return M > 16 && N % 128 == 0 && K % 64 == 0;
+}
+
+int launch_gemm_tc(const __half* A, const uint8_t* B, const __half* scale, __half* C, const __half* residual, int M,
+                   int N, int K, cudaStream_t stream)
+{
+    EET_CHECK(gemm_tc_supported(M, N, K), "tensor-core GEMM: needs M > 16, N %% 128 == 0, K %% 64 == 0");
+    EncodeTiledFn encode = encode_tiled_fn();
+    EET_CHECK(encode != nullptr, "tensor-core GEMM: cuTensorMapEncodeTiled is not available from the driver");
+    const int bn = (M > 128) ? 256 : (M > 64 ? 128 : 64);
+    CUtensorMap map;
+    const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)M};
+    const cuuint64_t strides[1] = {(cuuint64_t)K * sizeof(__half)};
+    const cuuint32_t box[2] = {64, (cuuint32_t)bn};
+    const cuuint32_t elem[2] = {1, 1};
+    const CUresult rc = encode(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<__half*>(A), dims, strides, box, elem,
+                               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    EET_CHECK(rc == CUDA_SUCCESS, "tensor-core GEMM: cuTensorMapEncodeTiled failed with code %d", (int)rc);
+    if (bn == 256) return launch_tc<256>(map, B, scale, C, residual, M, N, K, stream);
+    if (bn == 128) return launch_tc<128>(map, B, scale, C, residual, M, N, K, stream);
+    return launch_tc<64>(map, B, scale, C, residual, M, N, K, stream);
+}
+
+}  // namespace eet

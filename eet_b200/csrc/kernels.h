@@ -29,6 +29,7 @@ size_t skinny_sum_bytes(int M, int N);
 int launch_gemm_skinny(const GemmArgs& a, cudaStream_t stream);
 
 // gemm_tc.cu (tcgen05 / TMEM)
+bool gemm_tc_supported(int M, int N, int K);
 int launch_gemm_tc(const __half* A, const uint8_t* B, const __half* scale, __half* C, const __half* residual, int M,
                    int N, int K, cudaStream_t stream);
 
