@@ -24,6 +24,7 @@ SIGNATURES = {
     "eet_repack_ref_w8": (_i, [_vp, _i, _i, _vp, _vp]),
     "eet_gemm_w8a16_workspace_bytes": (_sz, [_i, _i, _i]),
     "eet_gemm_w8a16": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _vp, _i, _vp, _sz, _vp]),
+    "eet_gemm_w8a16_noalloc": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _vp, _i, _vp]),
     "eet_gemm_w8a16_accum": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp, _vp, _vp]),
     "eet_gemm_w8a16_finalize": (_i, [_vp, _vp, _vp, _vp, _i, _i, _vp]),
     "eet_rmsnorm_finalize": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _f, _vp]),

@@ -48,6 +48,7 @@ static inline bool aligned16(const void* p)
 #include "gemm_skinny.cu"
 #include "gemm_tc.cu"
 #include "glue.cu"
+#include "noalloc.cu"
 #include "quantize.cu"
 
 using namespace eet;
@@ -206,6 +207,19 @@ int eet_gemm_w8a16(const void* A, const void* packedB, const void* scale, void* 
             return rc;
     }
     return 0;
+}
+
+int eet_gemm_w8a16_noalloc(const void* A, const void* packedB, const void* scale, void* C, int M, int N, int K,
+                           const void* residual, int epilogue, void* stream)
+{
+    if (check_gemm("eet_gemm_w8a16_noalloc", A, packedB, M, N, K)) return 1;
+    if (M == 0) return 0;
+    EET_CHECK(scale && C && aligned16(C) && aligned16(scale) && aligned16(residual),
+              "eet_gemm_w8a16_noalloc: scale, C and residual must be 16-byte aligned buffers");
+    EET_CHECK(epilogue == 0 || epilogue == 1, "eet_gemm_w8a16_noalloc: unknown epilogue %d", epilogue);
+    EET_CHECK(epilogue != 1 || residual != nullptr, "eet_gemm_w8a16_noalloc: epilogue 1 needs a residual");
+    return gemm_w8a16_noalloc((const __half*)A, (const uint8_t*)packedB, (const __half*)scale, (__half*)C, M, N, K,
+                              epilogue == 1 ? (const __half*)residual : nullptr, (cudaStream_t)stream);
 }
 
 int eet_rmsnorm(const void* x, const void* gamma, void* y, int M, int n, float eps, void* stream)

@@ -33,6 +33,10 @@ bool gemm_tc_supported(int M, int N, int K);
 int launch_gemm_tc(const __half* A, const uint8_t* B, const __half* scale, __half* C, const __half* residual, int M,
                    int N, int K, cudaStream_t stream);
 
+// noalloc.cu
+int gemm_w8a16_noalloc(const __half* A, const uint8_t* B, const __half* scale, __half* C, int M, int N, int K,
+                       const __half* residual, cudaStream_t stream);
+
 // glue.cu
 int launch_rmsnorm(const __half* x, const __half* gamma, __half* y, int M, int n, float eps, cudaStream_t stream);
 int launch_finalize(float* sums, const __half* scale, const __half* residual, __half* C, int M, int N,

@@ -111,6 +111,21 @@ int eet_gemm_w8a16_accum(const void* A, const void* packedB, float* sums, int M,
                          float* sums2, void* stream);
 int eet_gemm_w8a16_finalize(float* sums, const void* scale, const void* residual, void* C, int M, int N, void* stream);
 
+/*
+ * eet_gemm_w8a16 for M <= 16 without a caller-provided scratch buffer.  It has no counterpart in the
+ * reference.  It exists for hosts that may not allocate device memory - a server that gave all of HBM to
+ * one arena at start-up, a plugin inside somebody else's process, a decode loop that cannot take the
+ * device-wide stall of cudaMalloc - and therefore cannot hand eet_gemm_w8a16 its zeroed fp32 scratch.
+ * The scratch is a fixed 2 MiB array inside the library's device image (held by every GPU that loads the
+ * library, until the process ends): M * N may not exceed 16 * 32768, M may not exceed 16; larger problems
+ * are refused with an error (for M > 16 eet_gemm_w8a16 needs no scratch anyway).  The call allocates
+ * nothing.  Its first use on a device looks up the array's device address, so make that first call outside
+ * any stream capture.  All calls on a device share the array: it is cleared at the start of each call, and
+ * two calls that overlap on the GPU (different streams) race.
+ */
+int eet_gemm_w8a16_noalloc(const void* A, const void* packedB, const void* scale, void* C, int M, int N, int K,
+                           const void* residual, int epilogue, void* stream);
+
 /* ------------------------------------------------------------------------------------------------
  * Kernels between the GEMMs
  * ---------------------------------------------------------------------------------------------- */
