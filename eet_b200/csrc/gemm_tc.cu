@@ -261,6 +261,204 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t* __rest
     }
 }
 
+// ---------------------------------------------------------------------------------------------------
+// Large-M variant: 256 channels x 256 tokens per CTA.  Two accumulators (one per 128-channel half) fill all
+// 512 TMEM columns, and every activation tile fetched from L2 feeds twice as many MMAs as in the kernel
+// above, which halves the L2 -> shared-memory traffic per flop.  The three data streams have their own rings
+// so that each can run as far ahead as its buffer allows:
+//   activations : 3 x 32 KiB, one 2-D TMA copy per k-block            (warp 0)
+//   int8 weights: 4 x 16 KiB, four 4 KiB bulk copies per k-block      (warp 6)
+//   fp16 weights: 3 x 16 KiB units of 128 channels x 64 k, written by warps 2-5, read by tcgen05.mma
+// ---------------------------------------------------------------------------------------------------
+constexpr int kTc2Threads = 224;
+constexpr int kTc2NX = 3, kTc2NW = 4, kTc2NH = 3;
+constexpr int kTc2XBytes = 256 * 128, kTc2WBytes = 4 * kTileBytes, kTc2HBytes = 128 * 128;
+constexpr int kTc2Smem = kTc2NX * kTc2XBytes + kTc2NW * kTc2WBytes + kTc2NH * kTc2HBytes;
+
+struct Tc2Smem {
+    uint64_t x_full[kTc2NX], x_empty[kTc2NX];
+    uint64_t w_full[kTc2NW], w_empty[kTc2NW];
+    uint64_t h_ready[kTc2NH], h_empty[kTc2NH];
+    uint64_t accum;
+    uint32_t tmem_base;
+    volatile int abort;
+};
+
+__global__ void __launch_bounds__(kTc2Threads, 1)
+gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t* __restrict__ Bw, const __half* __restrict__ scale,
+                __half* __restrict__ C, const __half* __restrict__ residual, int M, int N, int K)
+{
+    extern __shared__ __align__(1024) uint8_t tc_dyn[];
+    __shared__ Tc2Smem sm;
+    uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(tc_dyn) + 1023) & ~(uintptr_t)1023);
+    uint8_t* x_ring = base;                                   // 1024-byte aligned tiles (swizzled)
+    uint8_t* h_ring = base + kTc2NX * kTc2XBytes;             // 1024-byte aligned tiles (swizzled)
+    uint8_t* w_ring = h_ring + kTc2NH * kTc2HBytes;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n0 = blockIdx.x * 256;
+    const int m0 = blockIdx.y * 256;
+    const int KT = K / kTile;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kTc2NX; ++s) {
+            mbar_init(&sm.x_full[s], 1);
+            mbar_init(&sm.x_empty[s], 1);
+        }
+        for (int s = 0; s < kTc2NW; ++s) {
+            mbar_init(&sm.w_full[s], 1);
+            mbar_init(&sm.w_empty[s], 4);
+        }
+        for (int s = 0; s < kTc2NH; ++s) {
+            mbar_init(&sm.h_ready[s], 4);
+            mbar_init(&sm.h_empty[s], 1);
+        }
+        mbar_init(&sm.accum, 1);
+        sm.abort = 0;
+        mbar_fence_init();
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)),
+                     "r"(512u)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = sm.tmem_base;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ activation producer
+        if (lane == 0) {
+            for (int kb = 0; kb < KT; ++kb) {
+                const int s = kb % kTc2NX;
+                if (kb >= kTc2NX && !tc_wait(&sm.x_empty[s], ((kb / kTc2NX) - 1) & 1, &sm.abort)) break;
+                mbar_arrive_expect_tx(&sm.x_full[s], (uint32_t)kTc2XBytes);
+                tma_load_2d(x_ring + (size_t)s * kTc2XBytes, &tmap_x, kb * kTile, m0, &sm.x_full[s]);
+            }
+        }
+    }
+    else if (warp == 6) {
+        // ------------------------------------------------------------------ int8 weight producer
+        if (lane == 0) {
+            for (int kb = 0; kb < KT; ++kb) {
+                const int s = kb % kTc2NW;
+                if (kb >= kTc2NW && !tc_wait(&sm.w_empty[s], ((kb / kTc2NW) - 1) & 1, &sm.abort)) break;
+                mbar_arrive_expect_tx(&sm.w_full[s], (uint32_t)kTc2WBytes);
+                const uint8_t* w0 = Bw + ((size_t)(n0 / kTile) * KT + kb) * kTileBytes;
+                uint8_t* dst = w_ring + (size_t)s * kTc2WBytes;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    bulk_g2s(dst + i * kTileBytes, w0 + (size_t)i * KT * kTileBytes, kTileBytes, &sm.w_full[s]);
+                }
+            }
+        }
+    }
+    else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_idesc_f16(128, 256);
+            bool ok = true;
+            for (int kb = 0; kb < KT && ok; ++kb) {
+                const int sx = kb % kTc2NX;
+                if (!tc_wait(&sm.x_full[sx], (kb / kTc2NX) & 1, &sm.abort)) break;
+                const uint64_t b_desc = umma_desc_sw128(smem_u32(x_ring + (size_t)sx * kTc2XBytes));
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const int u = 2 * kb + h, su = u % kTc2NH;
+                    if (!tc_wait(&sm.h_ready[su], (u / kTc2NH) & 1, &sm.abort)) {
+                        ok = false;
+                        break;
+                    }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint64_t a_desc = umma_desc_sw128(smem_u32(h_ring + (size_t)su * kTc2HBytes));
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        umma_f16(tmem + (uint32_t)(h * 256), a_desc + (uint64_t)(2 * k), b_desc + (uint64_t)(2 * k), idesc,
+                                 (kb | k) != 0);
+                    }
+                    umma_commit(&sm.h_empty[su]);
+                }
+                if (ok) umma_commit(&sm.x_empty[sx]);
+            }
+            umma_commit(&sm.accum);
+        }
+    }
+    else {
+        // ------------------------------------------------------------------ transform warps, then epilogue
+        const int tw = threadIdx.x - 64;  // 0..127
+        bool ok = true;
+        for (int kb = 0; kb < KT && ok; ++kb) {
+            const int sw = kb % kTc2NW;
+            if (!tc_wait(&sm.w_full[sw], (kb / kTc2NW) & 1, &sm.abort)) break;
+            const uint8_t* w8 = w_ring + (size_t)sw * kTc2WBytes;
+#pragma unroll 1
+            for (int h = 0; h < 2; ++h) {
+                const int u = 2 * kb + h, su = u % kTc2NH;
+                if (u >= kTc2NH && !tc_wait(&sm.h_empty[su], ((u / kTc2NH) - 1) & 1, &sm.abort)) {
+                    ok = false;
+                    break;
+                }
+                uint8_t* wh = h_ring + (size_t)su * kTc2HBytes;
+#pragma unroll
+                for (int pass = 0; pass < 4; ++pass) {
+                    const int r = pass * 32 + (tw >> 2);   // channel row of this half, 0..127
+                    const int qd = tw & 3;
+                    const uint4 raw = *reinterpret_cast<const uint4*>(w8 + (h * 128 + r) * 64 + qd * 16);
+                    uint4 o0, o1;
+                    cvt_u8x4_to_f16x4(raw.x, o0.x, o0.y);
+                    cvt_u8x4_to_f16x4(raw.y, o0.z, o0.w);
+                    cvt_u8x4_to_f16x4(raw.z, o1.x, o1.y);
+                    cvt_u8x4_to_f16x4(raw.w, o1.z, o1.w);
+                    uint8_t* row = wh + r * 128;
+                    *reinterpret_cast<uint4*>(row + (((2 * qd) ^ (r & 7)) << 4)) = o0;
+                    *reinterpret_cast<uint4*>(row + (((2 * qd + 1) ^ (r & 7)) << 4)) = o1;
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&sm.h_ready[su]);
+            }
+            if (ok) {
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&sm.w_empty[sw]);
+            }
+        }
+
+        // ---- epilogue: TMEM lane = channel within the half, columns = tokens ----
+        if (tc_wait(&sm.accum, 0, &sm.abort)) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const int lane_base = (warp & 3) * 32;
+#pragma unroll 1
+            for (int h = 0; h < 2; ++h) {
+                const int n = n0 + h * 128 + lane_base + lane;
+                const float sc = __half2float(scale[n]);
+#pragma unroll 1
+                for (int c0 = 0; c0 < 256; c0 += 32) {
+                    if (m0 + c0 >= M) break;
+                    uint32_t v[32];
+                    tmem_ld32(tmem + ((uint32_t)lane_base << 16) + (uint32_t)(h * 256 + c0), v);
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const int m = m0 + c0 + j;
+                        if (m < M) {
+                            const size_t o = (size_t)m * N + n;
+                            __half r = __float2half(__uint_as_float(v[j]) * sc);
+                            if (residual != nullptr) r = __hadd(r, residual[o]);
+                            C[o] = r;
+                        }
+                    }
+                }
+            }
+        }
+    }
+
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
+    }
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -300,15 +498,19 @@ int launch_tc(const CUtensorMap& map, const uint8_t* B, const __half* scale, __h
 
 }  // namespace
 
+// Below this many tokens the skinny kernel (weights streamed once per 16-token chunk row, the chunk rows of
+// one launch sharing them through L2) is faster than a tensor-core tile that leaves most SMs idle.
+constexpr int kTcMinM = 65;
+
 bool gemm_tc_supported(int M, int N, int K)
 {
-    return M > 16 && N % 128 == 0 && K % 64 == 0;
+    return M >= kTcMinM && N % 128 == 0 && K % 64 == 0;
 }
 
 int launch_gemm_tc(const __half* A, const uint8_t* B, const __half* scale, __half* C, const __half* residual, int M,
                    int N, int K, cudaStream_t stream)
 {
-    EET_CHECK(gemm_tc_supported(M, N, K), "tensor-core GEMM: needs M > 16, N %% 128 == 0, K %% 64 == 0");
+    EET_CHECK(gemm_tc_supported(M, N, K), "tensor-core GEMM: needs M >= 65, N %% 128 == 0, K %% 64 == 0");
     EncodeTiledFn encode = encode_tiled_fn();
     EET_CHECK(encode != nullptr, "tensor-core GEMM: cuTensorMapEncodeTiled is not available from the driver");
     const int bn = (M > 128) ? 256 : (M > 64 ? 128 : 64);
@@ -321,6 +523,22 @@ int launch_gemm_tc(const __half* A, const uint8_t* B, const __half* scale, __hal
                                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     EET_CHECK(rc == CUDA_SUCCESS, "tensor-core GEMM: cuTensorMapEncodeTiled failed with code %d", (int)rc);
+    // the 256 x 256 tiles pay off once there are enough of them to fill the machine more than once
+    if (N % 256 == 0 && (long long)(N / 256) * ((M + 255) / 256) >= 200) {
+        static bool attr_set2[64] = {};
+        int dev = 0;
+        EET_CUDA(cudaGetDevice(&dev));
+        dev &= 63;
+        const size_t smem = (size_t)kTc2Smem + 1024;
+        if (!attr_set2[dev]) {
+            EET_CUDA(cudaFuncSetAttribute(gemm_tc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            attr_set2[dev] = true;
+        }
+        dim3 grid(N / 256, (M + 255) / 256);
+        gemm_tc2_kernel<<<grid, kTc2Threads, smem, stream>>>(map, B, scale, C, residual, M, N, K);
+        EET_LAUNCH_CHECK();
+        return 0;
+    }
     if (bn == 256) return launch_tc<256>(map, B, scale, C, residual, M, N, K, stream);
     if (bn == 128) return launch_tc<128>(map, B, scale, C, residual, M, N, K, stream);
     return launch_tc<64>(map, B, scale, C, residual, M, N, K, stream);
