@@ -392,10 +392,19 @@ def run_ours(args):
         line["cpu_baseline"] = {"value": round(tok_s, 3), "unit": UNIT, "cores": threads, "kind": "port",
                                 "sample": sample}
     if rank == 0:
-        print(json.dumps(line))
+        print(json.dumps(line), flush=True)
     if world > 1:
+        # CUDA graphs that captured NCCL kernels keep the communicator busy: drop them before tearing the
+        # process group down, and never let the teardown outlive the measurement by more than a few seconds
+        threading.Timer(20.0, lambda: os._exit(0)).start()
+        model.end_graph()
+        del model
+        import gc
+        gc.collect()
+        torch.cuda.synchronize()
         dist.barrier()
         dist.destroy_process_group()
+        os._exit(0)
 
 
 def main():
