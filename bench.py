@@ -368,7 +368,10 @@ def run_ours(args):
     gemms = time_gemm_shapes(model, BATCH)
     g_bytes = sum(v["bytes"] for v in gemms.values())
     g_time = sum(v["us"] for v in gemms.values()) * 1e-6
-    achieved = g_bytes / g_time / 1e9
+    dom = gemms["qkv"]   # the largest single launch of a layer: fused QKV projection
+    # dram__bytes_read.sum + dram__bytes_write.sum of one such launch at TP 1 (K=4096, N=12288, M=8), from the
+    # ncu capture summarised in profiles/gemm_skinny_m8_llama7b_shapes.md; scaled by the bytes of the shard
+    traffic = 50.81e6 * dom["bytes"] / 50620416.0
     line = {"metric": METRIC, "value": round(BATCH * K / t_dev, 2), "unit": UNIT, "n_gpus": world, "steps": K,
             "warmup": W, "ms_per_step": round(t_dev / K * 1e3, 4), "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "f16 activations x int8 weights, f32 accumulate", "data": "synthetic",
@@ -380,9 +383,14 @@ def run_ours(args):
                     "d2h_bytes_per_step": BATCH * 8, "ms_per_step": round(t_e2e / K * 1e3, 4)},
             "gpu_launches": kernel_launches_per_step(n_layers) * K,
             "clocks": clk.summary(), "clocks_e2e": clk_e2e.summary(), "device_status": status,
-            "roofline": {"bound": "hbm", "kernel": "gemm_skinny_kernel<1> (5 projection shapes x layers, M=8)",
-                         "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
-                         "frac": round(achieved / pk["hbm_gbs"], 4), "peak_source": pk["source"], "traffic": None,
+            "roofline": {"bound": "hbm",
+                         "kernel": f"gemm_skinny_kernel<1>, fused QKV projection K={dom['K']} N={dom['N']} M={BATCH}",
+                         "achieved": round(dom["gbs"], 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                         "frac": round(dom["gbs"] / pk["hbm_gbs"], 4), "peak_source": pk["source"],
+                         "traffic": round(traffic), "algorithmic_bytes": dom["bytes"],
+                         "launch_us": round(dom["us"], 2),
+                         "all_gemm_launches_of_a_layer": {"achieved": round(g_bytes / g_time / 1e9, 1),
+                                                          "frac": round(g_bytes / g_time / 1e9 / pk["hbm_gbs"], 4)},
                          "per_shape": {k: {"K": v["K"], "N": v["N"], "us": round(v["us"], 2), "gbs": round(v["gbs"], 1)}
                                        for k, v in gemms.items()}}}
     if world == 1 and not args.no_sweep:

@@ -153,3 +153,21 @@ def test_accumulate_and_fused_finalize_kernels():
     # without sums it is a plain RMSNorm of `residual`
     check(lib.eet_rmsnorm_finalize(None, None, resc.data_ptr(), None, gc.data_ptr(), xn.data_ptr(), M, N, 1e-6, stream))
     assert torch.allclose(xn.cpu().float(), ops.rmsnorm(res, gamma, 1e-6).float(), rtol=1e-3, atol=1e-3)
+
+
+@pytest.mark.parametrize("KN", [(5120, 15360), (5120, 13696), (13696, 5120), (8192, 24576), (8192, 22016), (22016, 8192)])
+def test_baichuan13b_and_llama65b_projection_shapes(KN):
+    """configs[3] / configs[4] layer shapes at full size: random activations against the fp32 oracle on the
+    decode batch of those configs capped at 16 rows, plus a prefill-sized batch through the tensor-core path
+    checked on sampled rows (the full fp32 product would take the CPU minutes)."""
+    K, N = KN
+    gen = torch.Generator().manual_seed(K + N)
+    q = torch.randint(-128, 128, (K, N), generator=gen, dtype=torch.int8)
+    s = (torch.rand(N, generator=gen) * 3e-4 + 1e-4).half()
+    x = torch.randn(16, K, generator=gen).half()
+    _check(_run(x, q, s), x, q, s)
+    xl = torch.randn(384, K, generator=gen).half()
+    y = _run(xl, q, s)
+    rows = torch.tensor([0, 1, 63, 64, 127, 128, 255, 256, 300, 383])
+    ref = ops.gemm_w8a16_fp32(xl[rows], q, s)
+    assert ((y[rows].double() - ref).abs() <= 1e-2 * ref.abs().amax(1, keepdim=True)).all()
