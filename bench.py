@@ -140,6 +140,7 @@ def rewind(model, step):
 
 
 def kernel_launches_per_step(n_layers):
+    # (with tensor parallelism two NCCL all-reduce kernels per layer come on top; they are not counted)
     # per layer: rmsnorm(+finalize), qkv gemm, decode attention, out gemm, rmsnorm(+finalize), gate+up gemm,
     # swiglu(+finalize), down gemm; per step: advance_steps + final rmsnorm(+finalize)
     return 8 * n_layers + 2

@@ -245,7 +245,7 @@ _DECODE_MAX_M = 16
 
 
 class deferred_epilogue:
-    """Context manager for a chain of decode-step ops of this module (M <= 16, no tensor parallelism): inside
+    """Context manager for a chain of decode-step ops of this module (M <= 16): inside
     it an attention / FFN op returns its output tensor *before* the last GEMM's epilogue has run, and the next
     op (attention, FFN or LayerNorm of this module) completes it in its RMSNorm kernel.  Outputs still
     unfinished when the context ends are completed then, so callers outside never see stale memory."""
@@ -384,10 +384,14 @@ class _MmhaBase:
         out = _pool.get("self_mask_attn_cache", d.batch_size * d.max_seq_len * d.hidden_units, torch.float16, d.device)
         out = out[: B * S * d.hidden_units].view(B * S, d.hidden_units)
         inp2d = inp.reshape(B * S, d.hidden_units)
-        if _defer[0] and B * S <= _DECODE_MAX_M and (d.tp is None or d.tp.size == 1):
+        if _defer[0] and B * S <= _DECODE_MAX_M:
             sums = _pool.zeros("out_sums", d.batch_size * d.hidden_units, torch.float32, d.device)
             sums = sums[: B * S * d.hidden_units].view(B * S, d.hidden_units)
             gemm_w8a16_accum(ctx2d, self.out_w, sums)
+            if d.tp is not None and d.tp.size > 1:
+                # row-parallel: the ranks' fp32 partial sums are added before scale, residual and rounding,
+                # so the result equals the single-GPU one up to fp32 summation order
+                d.tp.all_reduce(sums)
             _pending[out.data_ptr()] = _Pending(sums, self.out_s, inp2d, out)
         elif d.tp is None or d.tp.size == 1:
             gemm_w8a16(ctx2d, self.out_w, self.out_s, out=out, residual=inp2d)
@@ -593,9 +597,11 @@ class GatedFeedForwardNetworkInt8:
                 gemm_w8a16(xn, self.w0, self.s0, out=act)
                 gemm_w8a16(xn, self.w1, self.s1, out=lin)
                 check(lib.eet_swiglu(act.data_ptr(), lin.data_ptr(), M, self.d_ff, _stream()))
-            if deferred and add_residual and (d.tp is None or d.tp.size == 1):
+            if deferred and add_residual:
                 sums = _pool.zeros("down_sums", d.batch_size * h, torch.float32, d.device)[: M * h].view(M, h)
                 gemm_w8a16_accum(act, self.w_out, sums)
+                if d.tp is not None and d.tp.size > 1:
+                    d.tp.all_reduce(sums)   # row-parallel partial sums, see LlamaMmha._project
                 _pending[out.data_ptr()] = _Pending(sums, self.s_out, inp2d, out)
             elif d.tp is None or d.tp.size == 1:
                 gemm_w8a16(act, self.w_out, self.s_out, out=out, residual=inp2d if add_residual else None)
