@@ -232,11 +232,13 @@ def gemm_w8a16_accum(x, packed_w, sums, packed_w2=None, sums2=None):
 # ---------------------------------------------------------------------------------------------------
 class _Pending:
     """An op output whose fp16 values do not exist yet: fp32 GEMM sums + scale + residual.  The next op of
-    this module that receives the tensor finishes it inside its own first kernel."""
-    __slots__ = ("sums", "scale", "residual", "out")
+    this module that receives the tensor finishes it inside its own first kernel.  With tensor parallelism
+    `peer` = (PeerBuffers, which buffer): the sums are this rank's partial sums and the finishing kernel
+    also adds the other ranks' over NVLink."""
+    __slots__ = ("sums", "scale", "residual", "out", "peer")
 
-    def __init__(self, sums, scale, residual, out):
-        self.sums, self.scale, self.residual, self.out = sums, scale, residual, out
+    def __init__(self, sums, scale, residual, out, peer=None):
+        self.sums, self.scale, self.residual, self.out, self.peer = sums, scale, residual, out, peer
 
 
 _pending = {}
@@ -265,6 +267,8 @@ class deferred_epilogue:
 def flush_pending():
     for p in list(_pending.values()):
         M, N = p.sums.shape
+        if p.peer is not None:
+            p.peer[0].tp.all_reduce(p.sums)   # not consumed by an op of this module: plain NCCL path
         check(lib.eet_gemm_w8a16_finalize(p.sums.data_ptr(), p.scale.data_ptr(), _ptr(p.residual), p.out.data_ptr(),
                                           M, N, _stream()))
     _pending.clear()
@@ -274,7 +278,13 @@ def _norm_head(x2d, gamma, eps, xn):
     """RMSNorm at the head of a block; completes x first when it is a deferred output of the previous block."""
     M, n = x2d.shape
     p = _pending.pop(x2d.data_ptr(), None)
-    if p is not None:
+    if p is not None and p.peer is not None:
+        pb, which = p.peer
+        check(lib.eet_rmsnorm_finalize_tp(pb.sum_ptrs[which], pb.flag_ptrs, pb.tp.size, pb.tp.rank, pb.epochs.data_ptr(),
+                                          pb.buffer(1 - which, pb.ROWS).data_ptr(), p.scale.data_ptr(),
+                                          p.residual.data_ptr(), x2d.data_ptr(), gamma.data_ptr(), xn.data_ptr(), M, n,
+                                          eps, _stream()))
+    elif p is not None:
         check(lib.eet_rmsnorm_finalize(p.sums.data_ptr(), p.scale.data_ptr(), p.residual.data_ptr(), x2d.data_ptr(),
                                        gamma.data_ptr(), xn.data_ptr(), M, n, eps, _stream()))
     else:
@@ -385,14 +395,17 @@ class _MmhaBase:
         out = out[: B * S * d.hidden_units].view(B * S, d.hidden_units)
         inp2d = inp.reshape(B * S, d.hidden_units)
         if _defer[0] and B * S <= _DECODE_MAX_M:
-            sums = _pool.zeros("out_sums", d.batch_size * d.hidden_units, torch.float32, d.device)
-            sums = sums[: B * S * d.hidden_units].view(B * S, d.hidden_units)
-            gemm_w8a16_accum(ctx2d, self.out_w, sums)
+            peer = None
             if d.tp is not None and d.tp.size > 1:
-                # row-parallel: the ranks' fp32 partial sums are added before scale, residual and rounding,
-                # so the result equals the single-GPU one up to fp32 summation order
-                d.tp.all_reduce(sums)
-            _pending[out.data_ptr()] = _Pending(sums, self.out_s, inp2d, out)
+                # row-parallel: the ranks' fp32 partial sums are added before scale, residual and rounding -
+                # by the next block's first kernel, straight from the peers' memory
+                pb = d.tp.peer_buffers(d.hidden_units, d.device)
+                sums, peer = pb.buffer(0, B * S), (pb, 0)
+            else:
+                sums = _pool.zeros("out_sums", d.batch_size * d.hidden_units, torch.float32, d.device)
+                sums = sums[: B * S * d.hidden_units].view(B * S, d.hidden_units)
+            gemm_w8a16_accum(ctx2d, self.out_w, sums)
+            _pending[out.data_ptr()] = _Pending(sums, self.out_s, inp2d, out, peer)
         elif d.tp is None or d.tp.size == 1:
             gemm_w8a16(ctx2d, self.out_w, self.out_s, out=out, residual=inp2d)
         else:
@@ -598,11 +611,14 @@ class GatedFeedForwardNetworkInt8:
                 gemm_w8a16(xn, self.w1, self.s1, out=lin)
                 check(lib.eet_swiglu(act.data_ptr(), lin.data_ptr(), M, self.d_ff, _stream()))
             if deferred and add_residual:
-                sums = _pool.zeros("down_sums", d.batch_size * h, torch.float32, d.device)[: M * h].view(M, h)
-                gemm_w8a16_accum(act, self.w_out, sums)
+                peer = None
                 if d.tp is not None and d.tp.size > 1:
-                    d.tp.all_reduce(sums)   # row-parallel partial sums, see LlamaMmha._project
-                _pending[out.data_ptr()] = _Pending(sums, self.s_out, inp2d, out)
+                    pb = d.tp.peer_buffers(h, d.device)   # row-parallel partial sums, see LlamaMmha._project
+                    sums, peer = pb.buffer(1, M), (pb, 1)
+                else:
+                    sums = _pool.zeros("down_sums", d.batch_size * h, torch.float32, d.device)[: M * h].view(M, h)
+                gemm_w8a16_accum(act, self.w_out, sums)
+                _pending[out.data_ptr()] = _Pending(sums, self.s_out, inp2d, out, peer)
             elif d.tp is None or d.tp.size == 1:
                 gemm_w8a16(act, self.w_out, self.s_out, out=out, residual=inp2d if add_residual else None)
             else:

@@ -193,6 +193,134 @@ rmsnorm_finalize_kernel(float* __restrict__ sums, const __half* __restrict__ sca
     }
 }
 
+// Tensor-parallel form of rmsnorm_finalize_kernel: the all-reduce of a row-parallel projection fused into
+// the kernel that consumes it.  Every rank's GEMM has left its partial sums in a buffer that the other
+// ranks can read (peer memory over NVLink); a row's CTA first meets the same row's CTAs of the other ranks
+// at a flag barrier (each writes its epoch into every peer's flag array, then waits - for a bounded
+// number of polls - until all peers' epochs have arrived), then adds the `world` partial rows in fp32 in
+// rank order (so every rank computes bit-identical sums), applies scale and residual and normalises as the
+// single-GPU kernel does.  Two sum buffers alternate (attention output projection / FFN down projection):
+// this kernel zeroes the local copy of the one it does NOT read, which every rank finished reading before
+// it could pass this call's barrier.
+struct TpPeers {
+    const float* sums[8];   // the buffer to reduce, on every rank (index = rank)
+    int* flags[8];          // every rank's flag array [16 rows][8 ranks]
+    int world, rank;
+};
+
+constexpr uint32_t kTpSpinLimit = 1u << 22;
+
+__global__ void __launch_bounds__(1024)
+rmsnorm_finalize_tp_kernel(TpPeers peers, int* __restrict__ epochs, float* __restrict__ zero_local,
+                           const __half* __restrict__ scale, const __half* __restrict__ residual,
+                           __half* __restrict__ h_out, const __half* __restrict__ gamma, __half* __restrict__ xn_out,
+                           int n, float eps)
+{
+    __shared__ float red[32];
+    __shared__ float s_inv;
+    __shared__ int s_epoch;
+    pdl_launch_dependents();
+    pdl_wait();   // this rank's GEMM (and everything before it) is complete
+    const int row = blockIdx.x;
+    if (threadIdx.x == 0) {
+        s_epoch = epochs[row] + 1;
+        epochs[row] = s_epoch;
+        __threadfence_system();
+    }
+    __syncthreads();
+    const int epoch = s_epoch;
+    if (threadIdx.x < peers.world) {
+        // announce: my partial sums of this row are final
+        volatile int* theirs = peers.flags[threadIdx.x] + row * 8 + peers.rank;
+        *theirs = epoch;
+        // wait for the same announcement from rank threadIdx.x
+        volatile int* mine = peers.flags[peers.rank] + row * 8 + threadIdx.x;
+        uint32_t spins = 0;
+        while (*mine < epoch) {
+            if (++spins > kTpSpinLimit) {
+                g_device_status = 4;   // a peer never arrived: give up, the host reads the status word
+                break;
+            }
+        }
+        __threadfence_system();
+    }
+    __syncthreads();
+
+    const int nv = n >> 3;
+    const uint4* rr = reinterpret_cast<const uint4*>(residual + (size_t)row * n);
+    uint4 h[2];
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+        const int i = threadIdx.x + j * blockDim.x;
+        if (i < nv) {
+            // all ranks' 32 bytes are requested before any is used, so the NVLink round trips overlap;
+            // .cv loads: peer memory is read at its home, never from a stale local cache line
+            float4 pa[8], pb[8];
+#pragma unroll
+            for (int r = 0; r < 8; ++r) {
+                if (r < peers.world) {
+                    const float4* p = reinterpret_cast<const float4*>(peers.sums[r] + (size_t)row * n + (size_t)i * 8);
+                    pa[r] = __ldcv(p);
+                    pb[r] = __ldcv(p + 1);
+                }
+            }
+            float v[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) v[e] = 0.f;
+#pragma unroll
+            for (int r = 0; r < 8; ++r) {   // fixed rank order: every rank forms bit-identical sums
+                if (r < peers.world) {
+                    v[0] += pa[r].x; v[1] += pa[r].y; v[2] += pa[r].z; v[3] += pa[r].w;
+                    v[4] += pb[r].x; v[5] += pb[r].y; v[6] += pb[r].z; v[7] += pb[r].w;
+                }
+            }
+            const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+            float4* zp = reinterpret_cast<float4*>(zero_local + (size_t)row * n + (size_t)i * 8);
+            zp[0] = z;
+            zp[1] = z;
+            h[j] = rr[i];
+            const uint4 sc = reinterpret_cast<const uint4*>(scale)[i];
+            h[j] = finalize8(v, sc, &h[j]);
+            reinterpret_cast<uint4*>(h_out + (size_t)row * n)[i] = h[j];
+            const __half2* hh = reinterpret_cast<const __half2*>(&h[j]);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float2 f = __half22float2(hh[e]);
+                ss += f.x * f.x + f.y * f.y;
+            }
+        }
+    }
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        float t = (threadIdx.x < (blockDim.x >> 5)) ? red[threadIdx.x] : 0.f;
+        t = warp_sum(t);
+        if (threadIdx.x == 0) s_inv = rsqrtf(t / n + eps);
+    }
+    __syncthreads();
+    const float inv = s_inv;
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+        const int i = threadIdx.x + j * blockDim.x;
+        if (i < nv) {
+            const uint4 g = reinterpret_cast<const uint4*>(gamma)[i];
+            const __half2* hh = reinterpret_cast<const __half2*>(&h[j]);
+            const __half2* gh = reinterpret_cast<const __half2*>(&g);
+            uint4 o;
+            __half2* oh = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float2 f = __half22float2(hh[e]);
+                const float2 gg = __half22float2(gh[e]);
+                oh[e] = __float22half2_rn(make_float2(f.x * inv * gg.x, f.y * inv * gg.y));
+            }
+            reinterpret_cast<uint4*>(xn_out + (size_t)row * n)[i] = o;
+        }
+    }
+}
+
 // gate <- up * gate / (1 + exp(-gate)) with the reference's mix of precisions: exp in fp32 rounded to
 // fp16, the multiply, add and divide in fp16 (gated_silu<half>, csrc/core/activation_kernel.cu:106-124).
 __device__ __forceinline__ __half2 gated_silu2(__half2 g, __half2 u)
@@ -381,6 +509,32 @@ int launch_rmsnorm_finalize(float* sums, const __half* scale, const __half* resi
     if (threads > 1024) threads = 1024;
     EET_CUDA(launch_pdl(rmsnorm_finalize_kernel, dim3(M), dim3(threads), 0, stream, sums, scale, residual, h_out, gamma,
                         xn_out, n, eps));
+    return 0;
+}
+
+int launch_rmsnorm_finalize_tp(const float* const* peer_sums, int* const* peer_flags, int world, int rank, int* epochs,
+                               float* zero_local, const __half* scale, const __half* residual, __half* h_out,
+                               const __half* gamma, __half* xn_out, int M, int n, float eps, cudaStream_t stream)
+{
+    EET_CHECK(n % 8 == 0 && n > 0 && n <= 16384, "rmsnorm: hidden size %d must be a multiple of 8 and <= 16384", n);
+    EET_CHECK(world >= 1 && world <= 8 && rank >= 0 && rank < world, "tensor-parallel rmsnorm: bad world %d / rank %d",
+              world, rank);
+    EET_CHECK(M <= 16, "tensor-parallel rmsnorm: at most 16 rows (decode regime), got %d", M);
+    if (M == 0) return 0;
+    TpPeers peers = {};
+    for (int r = 0; r < world; ++r) {
+        EET_CHECK(peer_sums[r] != nullptr && peer_flags[r] != nullptr, "tensor-parallel rmsnorm: NULL peer pointer");
+        peers.sums[r] = peer_sums[r];
+        peers.flags[r] = peer_flags[r];
+    }
+    peers.world = world;
+    peers.rank = rank;
+    const int nv = n / 8;
+    int threads = ((nv + 1) / 2 + 31) / 32 * 32;
+    if (threads < 32) threads = 32;
+    if (threads > 1024) threads = 1024;
+    EET_CUDA(launch_pdl(rmsnorm_finalize_tp_kernel, dim3(M), dim3(threads), 0, stream, peers, epochs, zero_local, scale,
+                        residual, h_out, gamma, xn_out, n, eps));
     return 0;
 }
 

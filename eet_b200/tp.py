@@ -23,11 +23,71 @@ class TensorParallel:
         self.rank = dist.get_rank(group)
         self.size = dist.get_world_size(group)
 
+    def peer_buffers(self, hidden, device):
+        """Creates (once) the peer-addressable buffers of the fused all-reduce for this hidden size."""
+        if getattr(self, "_peer", None) is None or self._peer.hidden != hidden:
+            self._peer = PeerBuffers(self, hidden, device)
+        return self._peer
+
     def all_reduce(self, tensor):
         """In-place sum over the group on the current stream."""
         if self.size > 1:
             dist.all_reduce(tensor, op=dist.ReduceOp.SUM, group=self.group)
         return tensor
+
+
+class PeerBuffers:
+    """Memory of every rank that all ranks can address from their kernels: two fp32 partial-sum buffers
+    [rows][hidden] (attention-output / FFN-down projections alternate between them) and a flag array, shared
+    through CUDA IPC handles exchanged over the process group.  Lets the decode path replace
+    `NCCL all-reduce -> RMSNorm` by one kernel that reads the peers' partial sums over NVLink
+    (eet_rmsnorm_finalize_tp)."""
+
+    ROWS = 16
+
+    def __init__(self, tp, hidden, device):
+        import ctypes
+        device = torch.device(device)
+        if device.index is None:
+            device = torch.device("cuda", torch.cuda.current_device())
+        from torch.multiprocessing.reductions import reduce_tensor
+        self.tp, self.hidden = tp, hidden
+        n = self.ROWS * hidden
+        self.local_sums = torch.zeros(2 * n, dtype=torch.float32, device=device)
+        self.local_flags = torch.zeros(self.ROWS * 8, dtype=torch.int32, device=device)
+        self.epochs = torch.zeros(self.ROWS, dtype=torch.int32, device=device)
+        torch.cuda.synchronize(device)
+        mine = (reduce_tensor(self.local_sums), reduce_tensor(self.local_flags))
+        everyone = [None] * tp.size
+        dist.all_gather_object(everyone, mine, group=tp.group)
+        self.sums, self.flags = [], []
+        def open_on_my_device(reduced):
+            # The handle is opened with THIS rank's device current, so the peer's memory is mapped into this
+            # device's address space (the driver enables peer access for the mapping) - the arrangement NCCL's
+            # own P2P transport uses.  Opening it under the exporting device's index, which is what the stock
+            # tensor rebuild does, yields a mapping that kernels running on this device cannot touch.
+            fn, args = reduced
+            args = list(args)
+            args[6] = device.index   # storage_device
+            return fn(*args)
+
+        for r, (rs, rf) in enumerate(everyone):
+            if r == tp.rank:
+                self.sums.append(self.local_sums)
+                self.flags.append(self.local_flags)
+            else:
+                self.sums.append(open_on_my_device(rs))
+                self.flags.append(open_on_my_device(rf))
+        torch.cuda.synchronize(device)
+        dist.barrier(group=tp.group)
+        PtrArray = ctypes.c_void_p * tp.size
+        self._n = n
+        self.sum_ptrs = [PtrArray(*[t.data_ptr() + 4 * n * b for t in self.sums]) for b in (0, 1)]
+        self.flag_ptrs = PtrArray(*[t.data_ptr() for t in self.flags])
+
+    def buffer(self, which, rows):
+        """This rank's partial-sum buffer 0 (attention output projection) or 1 (FFN down projection)."""
+        return self.local_sums[which * self._n: which * self._n + rows * self.hidden].view(rows, self.hidden)
 
 
 def init_from_env(backend="nccl"):

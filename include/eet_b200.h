@@ -143,6 +143,20 @@ int eet_rmsnorm(const void* x, const void* gamma, void* y, int M, int n, float e
 int eet_rmsnorm_finalize(float* sums, const void* scale, const void* residual, void* h_out, const void* gamma,
                          void* xn_out, int M, int n, float eps, void* stream);
 
+/*
+ * Tensor-parallel form of eet_rmsnorm_finalize (decode, M <= 16): the all-reduce of a row-parallel projection
+ * fused into the kernel that consumes it.  peer_sums[r] / peer_flags[r] (host arrays of `world` device
+ * pointers, r = rank) address every rank's partial-sum buffer [M][n] fp32 and flag array (16 x 8 int32, zero
+ * at start) in memory all ranks can reach (CUDA IPC / peer access); epochs: 16 int32 of this rank, zero at
+ * start; zero_local: this rank's OTHER sum buffer, zeroed by this call (two buffers alternate between the
+ * attention-output and FFN-down projections).  The rows' CTAs of all ranks meet at a flag barrier with a
+ * bounded wait (status 4 in eet_device_status if a peer never arrives), add the partial rows in fp32 in rank
+ * order, then scale, residual, RMSNorm as eet_rmsnorm_finalize.  The reference is single-GPU: no counterpart.
+ */
+int eet_rmsnorm_finalize_tp(const float* const* peer_sums, int* const* peer_flags, int world, int rank, int* epochs,
+                            float* zero_local, const void* scale, const void* residual, void* h_out, const void* gamma,
+                            void* xn_out, int M, int n, float eps, void* stream);
+
 /* act_out = up * silu(gate) where gate = fp16(gate_sums * gate_scale), up = fp16(up_sums * up_scale) are the
  * unfinished products of eet_gemm_w8a16_accum; both sum buffers are zeroed.
  * Replaces: the epilogues of the gate / up GEMMs + gated_silu<half> (csrc/core/activation_kernel.cu:106-124). */
