@@ -11,8 +11,8 @@
 //    persistent CTAs per SM and CTA c owns an equal, contiguous run of tiles, i.e. one linear byte range
 //    of the weight array, whatever N and K are.
 //  * A producer warp feeds a ring of shared-memory stages with 1-D bulk copies (TMA engine,
-//    cp.async.bulk + mbarrier complete_tx, L2 evict-first hint): 24 KiB of weights (six tiles) per stage,
-//    three stages per CTA, two CTAs per SM.  The matching slice of the activations (a few KiB, L2
+//    cp.async.bulk + mbarrier complete_tx, L2 evict-first hint): 32 KiB of weights (eight tiles) per stage,
+//    two stages per CTA, two CTAs per SM (measured best among 16-40 KiB stages x 2-5 stages).  The matching slice of the activations (a few KiB, L2
 //    resident) is staged beside it by the consumer warps with plain 16-byte loads, one stage ahead.
 //  * Eight consumer warps share a stage by channel group and tile half: 16-byte shared loads deliver
 //    exactly the A fragments of mma.m16n8k16 (16 channels x 64 reduction indices per pair of loads),
@@ -46,10 +46,10 @@ namespace {
 constexpr int kConsumerWarps = 8;
 constexpr int kConsumerThreads = kConsumerWarps * 32;
 constexpr int kSkinnyThreads = kConsumerThreads + 32;
-constexpr int kStageTiles = 6;  // W8T64 tiles per stage: three for each half of the consumer warps
+constexpr int kStageTiles = 8;  // W8T64 tiles per stage: four for each half of the consumer warps
 constexpr int kStageWBytes = kStageTiles * kTileBytes;
 constexpr int kXRowBytes = kStageTiles * 128 + 16;  // one token's slice of a stage, padded: conflict-free loads
-constexpr int kMaxStages = 3;
+constexpr int kMaxStages = 2;
 constexpr int kSkinnyCtasPerSm = 2;
 
 __host__ __device__ constexpr int stage_bytes(int nb)
@@ -58,7 +58,8 @@ __host__ __device__ constexpr int stage_bytes(int nb)
 }
 __host__ __device__ constexpr int stage_count(int nb)
 {
-    return nb == 1 ? 3 : 2;  // 3 x 30.1 KiB or 2 x 36.3 KiB: two CTAs fit in one SM's shared memory
+    (void)nb;
+    return 2;  // 2 x 40.1 KiB (8 tokens) or 2 x 48.3 KiB (16 tokens): two CTAs fit in one SM's shared memory
 }
 
 struct SkinnySmem {
@@ -150,7 +151,7 @@ gemm_skinny_kernel(GemmArgs a)
     // activations, scratch and output belong to the dependency chain: wait for the preceding kernel
     pdl_wait();
 
-    // The four warps of a half stage the activations of their three tiles themselves: 16-byte global loads
+    // The four warps of a half stage the activations of their four tiles themselves: 16-byte global loads
     // (L2 hits) one stage ahead into registers, then into the stage's padded slab.
     constexpr int kHalfTiles = kStageTiles / 2;
     constexpr int kXChunks = 8 * NB * kHalfTiles * 8;          // 16-byte chunks per half and stage
