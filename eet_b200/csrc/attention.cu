@@ -31,8 +31,14 @@ constexpr int kAttnConsumerWarps = 4;
 constexpr int kAttnConsumerThreads = kAttnConsumerWarps * 32;
 constexpr int kAttnThreads = kAttnConsumerThreads + 32;  // + one producer warp
 constexpr int kHalfWarps = kAttnConsumerThreads / 16;
-constexpr int kAttnTile = 32;                             // time steps per shared-memory stage
-constexpr int kAttnStages = 2;
+#ifndef EET_ATTN_TILE
+#define EET_ATTN_TILE 32
+#define EET_ATTN_STAGES 2
+#define EET_ATTN_CTAS 5
+#endif
+constexpr int kAttnTile = EET_ATTN_TILE;                     // time steps per shared-memory stage
+constexpr int kAttnStages = EET_ATTN_STAGES;
+constexpr int kAttnCtasPerSm = EET_ATTN_CTAS;
 constexpr int kAttnRowBytes = 256;                        // D = 128 halves
 constexpr int kAttnStageBytes = 2 * kAttnTile * kAttnRowBytes;  // K tile + V tile
 
@@ -99,7 +105,7 @@ struct AttnSmem {
 // ring; five CTAs per SM keep ~160 KiB in flight.  Register-level loads of the same bytes stall on the
 // number of outstanding L1 misses long before HBM is busy.  Four consumer warps take a half-warp per time
 // step from shared memory.
-__global__ void __launch_bounds__(kAttnThreads, 5)
+__global__ void __launch_bounds__(kAttnThreads, kAttnCtasPerSm)
 decode_mha_kernel(DecodeAttnArgs a)
 {
     constexpr int D = 128;
@@ -373,100 +379,224 @@ decode_mha_kernel(DecodeAttnArgs a)
 // Prefill self-attention, causal with optional left padding (LLaMA) or ALiBi bias (Baichuan-13B).
 // Reference: q_k_mul + qk_softmax + attn_v_mul + transpose of LlamaMmha::forward_full
 // (csrc/op/llama_mmha.cpp:354-426; softmax_kernel_gpt2 csrc/core/gpt2_self_softmax.cu:8-57; ALiBi
-// variant masked_softmax_kernel :161-240).  The reference materialises [B,H,S,S] scores; this kernel is
-// blockwise: a CTA takes 16 consecutive queries of one (batch, head), stages 32 keys/values at a time in
-// shared memory and each warp runs the same online softmax as the decode kernel for its query.
-// Scores are rounded to fp16 where the reference stores them in fp16; probabilities are kept in fp32.
-constexpr int kPfQueries = 16;
-constexpr int kPfKeys = 32;
+// variant masked_softmax_kernel :161-240).  The reference materialises [B,H,S,S] scores in fp16 and runs
+// two cuBLAS batched GEMMs around a row-serial softmax; this kernel is blockwise (no S x S buffer):
+// a CTA takes 64 consecutive queries of one (batch, head), four warps of 16 query rows each; K and V of 64
+// keys at a time are staged in shared memory (cp.async, 16-byte chunks XOR-swizzled so ldmatrix is
+// conflict-free, double buffered); Q.K^T and P.V run on the tensor cores (mma.sync m16n8k16, fp16 in, fp32
+// accumulate) with the online softmax between them in registers.  Key blocks above the diagonal are
+// never visited.
+// Numerics kept: scores are scaled by the fp16-rounded 1/sqrt(D) and rounded to fp16 where the reference
+// stores them in fp16, the ALiBi bias is added in fp32 after that rounding, probabilities enter P.V as
+// fp16 (the reference's score buffer is fp16 too), denominator + 1e-6, rows above the left padding are
+// zero.
+constexpr int kPfQ = 64;         // queries per CTA
+constexpr int kPfK = 64;         // keys per shared-memory block
+constexpr int kPfThreads = 128;
+constexpr int kPfTileBytes = 64 * 256;   // 64 rows of 128 halves
 
-__global__ void __launch_bounds__(kPfQueries * 32)
+__device__ __forceinline__ uint32_t pf_swz(int row, int chunk)
+{
+    return (uint32_t)(row * 256 + ((chunk ^ (row & 7)) << 4));
+}
+
+__device__ __forceinline__ void cp_async16(uint32_t smem_addr, const void* gptr, bool valid)
+{
+    const int bytes = valid ? 16 : 0;   // src-size 0 zero-fills the destination
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_addr), "l"(gptr), "r"(bytes) : "memory");
+}
+
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3)
+{
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3)
+{
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+
+__device__ __forceinline__ uint32_t pack_half2(float a, float b)
+{
+    const __half2 h = __floats2half2_rn(a, b);
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+__global__ void __launch_bounds__(kPfThreads)
 prefill_mha_kernel(const __half* __restrict__ q, const __half* __restrict__ kcache, const __half* __restrict__ vcache,
                    __half* __restrict__ ctx, int S, int H, int T_max, const int64_t* __restrict__ pad_len,
                    const __half* __restrict__ alibi, int alibi_stride)
 {
     constexpr int D = 128;
-    __shared__ __align__(16) uint4 s_k[kPfKeys][D / 8];
-    __shared__ __align__(16) uint4 s_v[kPfKeys][D / 8];
+    extern __shared__ __align__(128) uint8_t pf_smem[];   // Q tile | K[2] | V[2]
+    const uint32_t sQ = smem_u32(pf_smem);
+    const uint32_t sK = sQ + kPfTileBytes;
+    const uint32_t sV = sK + 2 * kPfTileBytes;
     const int bh = blockIdx.y;
     const int b = bh / H, h = bh % H;
-    const int i0 = blockIdx.x * kPfQueries;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int sub = lane >> 4, hl = lane & 15;  // two half-warps per query: even / odd keys
-    const int i = i0 + warp;                    // this warp's query row
-    const int pad = pad_len ? (int)pad_len[b] : 0;
+    const int qb = blockIdx.x;
+    const int i0 = qb * kPfQ;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int pad = (pad_len != nullptr && alibi == nullptr) ? (int)pad_len[b] : 0;
     const size_t cache_row0 = ((size_t)b * H + h) * T_max;
-    const uint4* kc = reinterpret_cast<const uint4*>(kcache + cache_row0 * D);
-    const uint4* vc = reinterpret_cast<const uint4*>(vcache + cache_row0 * D);
+    const __half* qbase = q + (((size_t)b * H + h) * S) * D;
+    const __half* kbase = kcache + cache_row0 * D;
+    const __half* vbase = vcache + cache_row0 * D;
 
-    float qf[8];
-    if (i < S) {
-        const uint4 qv = reinterpret_cast<const uint4*>(q + (((size_t)b * H + h) * S + i) * D)[hl];
-        const __half2* qh = reinterpret_cast<const __half2*>(&qv);
+    auto load_tile = [&](uint32_t sdst, const __half* gsrc, int row0, int row_limit) {
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            const float2 f = __half22float2(qh[e]);
-            qf[2 * e] = f.x;
-            qf[2 * e + 1] = f.y;
+        for (int it = 0; it < 8; ++it) {
+            const int e = tid + it * kPfThreads;   // 1024 chunks of 16 bytes
+            const int r = e >> 4, c = e & 15;
+            const bool ok = (row0 + r) < row_limit;
+            cp_async16(sdst + pf_swz(r, c), gsrc + (size_t)(ok ? row0 + r : 0) * D + c * 8, ok);
         }
-    }
+    };
+
+    const int kb_first = pad / kPfK;                       // key blocks left of the padding are skipped
+    const int kb_last = min(qb, (S - 1) / kPfK);           // causal: nothing above the diagonal block
+    load_tile(sQ, qbase, i0, S);
+    load_tile(sK, kbase, kb_first * kPfK, S);
+    load_tile(sV, vbase, kb_first * kPfK, S);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+
+    float o[16][4];
+#pragma unroll
+    for (int n = 0; n < 16; ++n)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) o[n][c] = 0.f;
+    float m_run[2] = {-1e20f, -1e20f}, l_run[2] = {0.f, 0.f};
     const float scalar = __half2float(__float2half(sqrtf(1.0f / D)));
-    OnlineState st;
-    st.m = -1e20f;
-    st.l = 0.f;
-#pragma unroll
-    for (int e = 0; e < 8; ++e) st.acc[e] = 0.f;
+    const int row_a = i0 + warp * 16 + g, row_b = row_a + 8;   // this lane's two query rows
 
-    const int j_hi = min(S, i0 + kPfQueries);  // keys needed by the last query of the tile
-    const int j_lo = (alibi ? 0 : pad) / kPfKeys * kPfKeys;
-    for (int j0 = j_lo; j0 < j_hi; j0 += kPfKeys) {
-        __syncthreads();
-        for (int e = threadIdx.x; e < kPfKeys * (D / 8); e += blockDim.x) {
-            const int r = e / (D / 8), c = e % (D / 8);
-            if (j0 + r < S) {
-                s_k[r][c] = __ldg(kc + (size_t)(j0 + r) * (D / 8) + c);
-                s_v[r][c] = __ldg(vc + (size_t)(j0 + r) * (D / 8) + c);
-            }
+    uint32_t qf[8][4];
+    bool q_loaded = false;
+
+    for (int kb = kb_first; kb <= kb_last; ++kb) {
+        const int buf = (kb - kb_first) & 1;
+        if (kb < kb_last) {   // prefetch the next key block into the other buffer
+            load_tile(sK + (buf ^ 1) * kPfTileBytes, kbase, (kb + 1) * kPfK, S);
+            load_tile(sV + (buf ^ 1) * kPfTileBytes, vbase, (kb + 1) * kPfK, S);
+            asm volatile("cp.async.commit_group;" ::: "memory");
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        }
+        else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
         }
         __syncthreads();
-        if (i < S) {
-#pragma unroll 4
-            for (int r = sub; r < kPfKeys; r += 2) {
-                const int j = j0 + r;
-                if (j <= i && (alibi != nullptr || j >= pad)) {
-                    float s = half_warp_sum(dot8(s_k[r][hl], qf)) * scalar;
-                    s = __half2float(__float2half(s));
-                    if (alibi != nullptr) {
-                        s += __half2float(alibi[((size_t)h * alibi_stride + i) * alibi_stride + j]);
-                    }
-                    online_update(st, s, s_v[r][hl]);
+        if (!q_loaded) {
+            // A fragments of this warp's 16 query rows for the 8 k-steps of D = 128
+#pragma unroll
+            for (int kk = 0; kk < 8; ++kk) {
+                ldsm_x4(sQ + pf_swz(warp * 16 + (lane & 15), kk * 2 + (lane >> 4)), qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3]);
+            }
+            q_loaded = true;
+        }
+        const uint32_t kt = sK + buf * kPfTileBytes, vt = sV + buf * kPfTileBytes;
+
+        // ---- S = Q K^T for 64 keys: 8 n-tiles of 8 keys ----
+        float sc[8][4];
+#pragma unroll
+        for (int n = 0; n < 8; ++n)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) sc[n][c] = 0.f;
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+#pragma unroll
+            for (int np = 0; np < 4; ++np) {   // two n-tiles (16 keys) per ldmatrix.x4
+                uint32_t b0, b1, b2, b3;
+                const int krow = np * 16 + (lane & 7) + ((lane >> 4) << 3);
+                const int chunk = kk * 2 + ((lane >> 3) & 1);
+                ldsm_x4(kt + pf_swz(krow, chunk), b0, b1, b2, b3);
+                mma_m16n8k16(sc[2 * np], qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3], b0, b1);
+                mma_m16n8k16(sc[2 * np + 1], qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3], b2, b3);
+            }
+        }
+
+        // ---- scale, fp16 rounding, bias, masks; online softmax ----
+        float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int n = 0; n < 8; ++n) {
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const int i = (c < 2) ? row_a : row_b;
+                const int j = kb * kPfK + n * 8 + 2 * t + (c & 1);
+                float v = __half2float(__float2half(sc[n][c] * scalar));
+                if (alibi != nullptr && i < S && j <= i) {
+                    v += __half2float(alibi[((size_t)h * alibi_stride + i) * alibi_stride + j]);
                 }
+                v = (j <= i && j >= pad && j < S) ? v : -INFINITY;
+                sc[n][c] = v;
+                mx[c >> 1] = fmaxf(mx[c >> 1], v);
             }
         }
-    }
-    if (i >= S) return;
-    // merge the two half-warps of the query
-    const float m_o = __shfl_xor_sync(0xffffffffu, st.m, 16);
-    const float l_o = __shfl_xor_sync(0xffffffffu, st.l, 16);
-    const float m = fmaxf(st.m, m_o);
-    const float c_self = __expf(st.m - m), c_oth = __expf(m_o - m);
-    const float l = st.l * c_self + l_o * c_oth;
-    float out[8];
+        float corr[2];
 #pragma unroll
-    for (int e = 0; e < 8; ++e) {
-        const float o = __shfl_xor_sync(0xffffffffu, st.acc[e], 16);
-        out[e] = st.acc[e] * c_self + o * c_oth;
-    }
-    if (sub == 0) {
-        // rows above the left padding are zeroed by the reference (gpt2_self_softmax.cu:24-30)
-        const bool zero_row = (alibi == nullptr) && (i < pad);
-        const float inv = zero_row ? 0.f : 1.0f / (l + 1e-6f);
-        uint4 o;
-        __half2* oh = reinterpret_cast<__half2*>(&o);
+        for (int r = 0; r < 2; ++r) {
+            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+            const float m_new = fmaxf(m_run[r], mx[r]);
+            corr[r] = __expf(m_run[r] - m_new);
+            m_run[r] = m_new;
+            l_run[r] *= corr[r];
+        }
+        uint32_t pfrag[4][4];   // P as A fragments: 4 k-steps of 16 keys
 #pragma unroll
-        for (int e = 0; e < 4; ++e) oh[e] = __floats2half2_rn(out[2 * e] * inv, out[2 * e + 1] * inv);
-        // context layout [B][S][H*D], ready for the output projection (transpose, llama_mmha.cpp:418-426)
-        reinterpret_cast<uint4*>(ctx + (((size_t)b * S + i) * H + h) * D)[hl] = o;
+        for (int n = 0; n < 8; ++n) {
+            const float p0 = __expf(sc[n][0] - m_run[0]), p1 = __expf(sc[n][1] - m_run[0]);
+            const float p2 = __expf(sc[n][2] - m_run[1]), p3 = __expf(sc[n][3] - m_run[1]);
+            l_run[0] += p0 + p1;
+            l_run[1] += p2 + p3;
+            pfrag[n >> 1][(n & 1) * 2] = pack_half2(p0, p1);
+            pfrag[n >> 1][(n & 1) * 2 + 1] = pack_half2(p2, p3);
+        }
+#pragma unroll
+        for (int n = 0; n < 16; ++n) {
+            o[n][0] *= corr[0];
+            o[n][1] *= corr[0];
+            o[n][2] *= corr[1];
+            o[n][3] *= corr[1];
+        }
+
+        // ---- O += P V: k-steps of 16 keys, 16 n-tiles of 8 head dims ----
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) {
+#pragma unroll
+            for (int dp = 0; dp < 8; ++dp) {   // two d-tiles (16 dims) per ldmatrix.x4.trans
+                uint32_t b0, b1, b2, b3;
+                const int vrow = kk * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
+                const int chunk = dp * 2 + (lane >> 4);
+                ldsm_x4_trans(vt + pf_swz(vrow, chunk), b0, b1, b2, b3);
+                mma_m16n8k16(o[2 * dp], pfrag[kk][0], pfrag[kk][1], pfrag[kk][2], pfrag[kk][3], b0, b1);
+                mma_m16n8k16(o[2 * dp + 1], pfrag[kk][0], pfrag[kk][1], pfrag[kk][2], pfrag[kk][3], b2, b3);
+            }
+        }
+        __syncthreads();   // all warps are done with this buffer before the next prefetch overwrites it
+    }
+
+    asm volatile("cp.async.wait_group 0;" ::: "memory");   // nothing in flight at exit when no key block was visited
+
+    // ---- normalise and store: context layout [B][S][H*D] (the transpose of llama_mmha.cpp:418-426) ----
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
+        l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int i = r ? row_b : row_a;
+        if (i < S) {
+            // rows above the left padding are zeroed by the reference (gpt2_self_softmax.cu:24-30)
+            const float inv = (i < pad) ? 0.f : 1.0f / (l_run[r] + 1e-6f);
+            __half* dst = ctx + (((size_t)b * S + i) * H + h) * D;
+#pragma unroll
+            for (int n = 0; n < 16; ++n) {
+                *reinterpret_cast<uint32_t*>(dst + n * 8 + 2 * t) = pack_half2(o[n][2 * r] * inv, o[n][2 * r + 1] * inv);
+            }
+        }
     }
 }
 
@@ -482,7 +612,7 @@ int launch_decode_mha(const DecodeAttnArgs& a, cudaStream_t stream)
     if (splits == 0) {
         // as many CTAs as fit on the machine at once (5 per SM); at least 64 time steps per CTA
         const int len = a.step_dev ? a.T_max : a.step;
-        const int room = 5 * sm_count() / (a.B * a.H);
+        const int room = kAttnCtasPerSm * sm_count() / (a.B * a.H);
         splits = 1;
         while (splits < 8 && splits * 2 <= room && len / (splits * 2) >= 64) splits *= 2;
     }
@@ -491,6 +621,17 @@ int launch_decode_mha(const DecodeAttnArgs& a, cudaStream_t stream)
     cfg.gridDim = dim3(splits, a.B * a.H, 1);
     cfg.blockDim = dim3(kAttnThreads, 1, 1);
     cfg.dynamicSmemBytes = kAttnStages * kAttnStageBytes;
+    if (kAttnStages * kAttnStageBytes > 48 * 1024) {
+        static bool attr_set[64] = {};
+        int dev = 0;
+        EET_CUDA(cudaGetDevice(&dev));
+        dev &= 63;
+        if (!attr_set[dev]) {
+            EET_CUDA(cudaFuncSetAttribute(decode_mha_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          kAttnStages * kAttnStageBytes));
+            attr_set[dev] = true;
+        }
+    }
     cfg.stream = stream;
     cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -512,9 +653,18 @@ int launch_prefill_mha(const __half* q, const __half* kcache, const __half* vcac
     EET_CHECK(D == 128, "prefill attention: head size %d is not supported (128 only)", D);
     EET_CHECK(S <= T_max, "prefill attention: prompt length %d exceeds the cache length %d", S, T_max);
     if (B == 0 || S == 0) return 0;
-    dim3 grid((S + kPfQueries - 1) / kPfQueries, B * H);
-    prefill_mha_kernel<<<grid, kPfQueries * 32, 0, stream>>>(q, kcache, vcache, ctx, S, H, T_max, pad_len, alibi,
-                                                            alibi_stride);
+    static bool attr_set[64] = {};
+    int dev = 0;
+    EET_CUDA(cudaGetDevice(&dev));
+    dev &= 63;
+    const int smem = 5 * kPfTileBytes;
+    if (!attr_set[dev]) {
+        EET_CUDA(cudaFuncSetAttribute(prefill_mha_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        attr_set[dev] = true;
+    }
+    dim3 grid((S + kPfQ - 1) / kPfQ, B * H);
+    prefill_mha_kernel<<<grid, kPfThreads, smem, stream>>>(q, kcache, vcache, ctx, S, H, T_max, pad_len, alibi,
+                                                          alibi_stride);
     EET_LAUNCH_CHECK();
     return 0;
 }
