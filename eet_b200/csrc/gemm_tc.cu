@@ -124,6 +124,46 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32])
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+// Epilogue of one block of 128 channels x 32 tokens.  After tcgen05.ld every epilogue thread holds the 32
+// token sums of ONE channel, while the output is channel-contiguous; the block therefore goes through a
+// [32 tokens][128 channels] fp16 staging tile in shared memory (the operand rings are idle by then) and
+// leaves as 16-byte stores of whole 256-byte row segments, with the residual fetched the same way and all
+// four residual loads of a thread in flight before the first add.  Two staging tiles alternate so one named
+// barrier per block is enough.  Called by all 128 epilogue threads.
+constexpr int kEpiStageHalves = 32 * 128;
+
+__device__ __forceinline__ void epilogue_block(const uint32_t (&v)[32], float sc, __half* stage, int channel, int tw,
+                                               __half* C, const __half* residual, int m_first, int M, int N,
+                                               int n_first)
+{
+#pragma unroll
+    for (int j = 0; j < 32; ++j) stage[j * 128 + channel] = __float2half(__uint_as_float(v[j]) * sc);
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    uint4 res[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int idx = tw + i * 128, row = idx >> 4, ch8 = idx & 15;
+        res[i] = make_uint4(0u, 0u, 0u, 0u);
+        if (residual != nullptr && m_first + row < M) {
+            res[i] = *reinterpret_cast<const uint4*>(residual + (size_t)(m_first + row) * N + n_first + ch8 * 8);
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int idx = tw + i * 128, row = idx >> 4, ch8 = idx & 15;
+        if (m_first + row < M) {
+            uint4 o = *reinterpret_cast<const uint4*>(stage + row * 128 + ch8 * 8);
+            if (residual != nullptr) {
+                __half2* oh = reinterpret_cast<__half2*>(&o);
+                const __half2* rh = reinterpret_cast<const __half2*>(&res[i]);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) oh[e] = __hadd2(oh[e], rh[e]);
+            }
+            *reinterpret_cast<uint4*>(C + (size_t)(m_first + row) * N + n_first + ch8 * 8) = o;
+        }
+    }
+}
+
 template<int BN>
 __global__ void __launch_bounds__(kTcThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t* __restrict__ Bw, const __half* __restrict__ scale,
@@ -230,26 +270,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t* __rest
         }
 
         // ---- epilogue: TMEM lane = channel, columns = tokens ----
-        if (tc_wait(&sm.accum, 0, &sm.abort)) {
+        // every epilogue warp gets here (the waits are bounded); the barrier makes the abort decision uniform
+        tc_wait(&sm.accum, 0, &sm.abort);
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (sm.abort == 0) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const int lane_base = (warp & 3) * 32;        // the TMEM lanes this warp may read
-            const int n = n0 + lane_base + lane;
-            const float sc = __half2float(scale[n]);
+            const float sc = __half2float(scale[n0 + lane_base + lane]);
+            __half* stage = reinterpret_cast<__half*>(ring);
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 32) {
                 if (m0 + c0 >= M) break;
                 uint32_t v[32];
                 tmem_ld32(tmem + ((uint32_t)lane_base << 16) + (uint32_t)c0, v);
-#pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    const int m = m0 + c0 + j;
-                    if (m < M) {
-                        const size_t o = (size_t)m * N + n;
-                        __half r = __float2half(__uint_as_float(v[j]) * sc);
-                        if (residual != nullptr) r = __hadd(r, residual[o]);
-                        C[o] = r;
-                    }
-                }
+                epilogue_block(v, sc, stage + ((c0 >> 5) & 1) * kEpiStageHalves, lane_base + lane, tw, C, residual,
+                               m0 + c0, M, N, n0);
             }
         }
     }
@@ -425,28 +460,24 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t* __res
         }
 
         // ---- epilogue: TMEM lane = channel within the half, columns = tokens ----
-        if (tc_wait(&sm.accum, 0, &sm.abort)) {
+        // every epilogue warp gets here (the waits are bounded); the barrier makes the abort decision uniform
+        tc_wait(&sm.accum, 0, &sm.abort);
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (sm.abort == 0) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const int lane_base = (warp & 3) * 32;
+            __half* stage = reinterpret_cast<__half*>(x_ring);
+            int blk = 0;
 #pragma unroll 1
             for (int h = 0; h < 2; ++h) {
-                const int n = n0 + h * 128 + lane_base + lane;
-                const float sc = __half2float(scale[n]);
+                const float sc = __half2float(scale[n0 + h * 128 + lane_base + lane]);
 #pragma unroll 1
-                for (int c0 = 0; c0 < 256; c0 += 32) {
+                for (int c0 = 0; c0 < 256; c0 += 32, ++blk) {
                     if (m0 + c0 >= M) break;
                     uint32_t v[32];
                     tmem_ld32(tmem + ((uint32_t)lane_base << 16) + (uint32_t)(h * 256 + c0), v);
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        const int m = m0 + c0 + j;
-                        if (m < M) {
-                            const size_t o = (size_t)m * N + n;
-                            __half r = __float2half(__uint_as_float(v[j]) * sc);
-                            if (residual != nullptr) r = __hadd(r, residual[o]);
-                            C[o] = r;
-                        }
-                    }
+                    epilogue_block(v, sc, stage + (blk & 1) * kEpiStageHalves, lane_base + lane, tw, C, residual, m0 + c0,
+                                   M, N, n0 + h * 128);
                 }
             }
         }
