@@ -217,6 +217,18 @@ def gemm_w8a16(x, packed_w, scale, out=None, residual=None):
     return out
 
 
+def _linear(x, w, scale, out, residual=None):
+    """One projection of an op: W8A16 when w is int8 (packed), else the fp16 twin - w fp16 [K, N] row-major
+    through cuBLAS, as the reference's is_int8 == false branches do (cublasGemmEx in
+    csrc/op/llama_mmha.cpp:288-310, csrc/op/gated_ffn.cpp), then the residual with this library's kernel."""
+    if w.dtype == torch.int8:
+        return gemm_w8a16(x, w, scale, out=out, residual=residual)
+    torch.matmul(x, w, out=out)
+    if residual is not None:
+        check(lib.eet_add_residual(out.data_ptr(), residual.data_ptr(), out.numel(), _stream()))
+    return out
+
+
 def gemm_w8a16_accum(x, packed_w, sums, packed_w2=None, sums2=None):
     """sums[M, N] += x[M, K] @ q (unscaled int8 values); optionally the same for a second weight in the same
     launch.  The decode-regime half of gemm_w8a16: whoever reads `sums` applies scale / residual."""
@@ -298,7 +310,8 @@ def _norm_head(x2d, gamma, eps, xn):
 class MetaDesc:
     """Shape / dtype descriptor handed to every op (csrc/op/meta_desc.hpp:9-101, binding
     csrc/py11/eet2py.cpp:26-42).  max_seq_len is the prompt cap (sizes scratch), max_full_seq_len the
-    KV-cache length.  Only dtype=torch.float16 with is_int8=True is served by this library.
+    KV-cache length.  dtype must be torch.float16; is_int8 selects packed int8 weights (the accelerated
+    path) or plain fp16 weights (the twin ops, GEMMs through cuBLAS like the reference).
 
     `tp` (not in the reference) is an optional eet_b200.tp.TensorParallel handle: the ops then treat their
     weights as this rank's shard (head_num / d_ff already divided by the caller) and all-reduce the output
@@ -328,9 +341,15 @@ class MetaDesc:
         self.is_int8 = bool(is_int8)
         self.tp = tp
 
-    def _require_int8_half(self, who):
-        if self.dtype != torch.float16 or not self.is_int8:
-            raise RuntimeError(f"{who}: this library serves dtype=torch.float16 with is_int8=True only")
+    def _require_half(self, who, int8=None):
+        if self.dtype != torch.float16:
+            raise RuntimeError(f"{who}: this library serves dtype=torch.float16 only")
+        if int8 is not None and self.is_int8 != int8:
+            raise RuntimeError(f"{who}: MetaDesc.is_int8 must be {int8} for this op")
+
+    @property
+    def weight_dtype(self):
+        return torch.int8 if self.is_int8 else torch.float16
 
 
 def _rmsnorm(x2d, gamma, eps, out):
@@ -351,7 +370,7 @@ class _MmhaBase:
 
     def __init__(self, desc, QKV_weights, QKV_scale, Q_bias, K_bias, V_bias, Output_weights, Output_scale,
                  Output_bias, layernorm_weights, layernorm_bias):
-        desc._require_int8_half(type(self).__name__)
+        desc._require_half(type(self).__name__)
         for name, b in (("Q_bias", Q_bias), ("K_bias", K_bias), ("V_bias", V_bias), ("Output_bias", Output_bias),
                         ("layernorm_bias", layernorm_bias)):
             if b is not None and b.numel() != 0:
@@ -373,8 +392,9 @@ class _MmhaBase:
             raise RuntimeError("attention: only head size 128 is supported")
         for t, shape, what in ((self.qkv_w, (desc.hidden_units, 3 * self.inner_dim), "QKV_weights"),
                                (self.out_w, (self.inner_dim, desc.hidden_units), "Output_weights")):
-            if tuple(t.shape) != shape or t.dtype != torch.int8 or not t.is_cuda:
-                raise RuntimeError(f"{what} must be a CUDA int8 tensor of shape {shape}, got {tuple(t.shape)} {t.dtype}")
+            if tuple(t.shape) != shape or t.dtype != desc.weight_dtype or not t.is_cuda or not t.is_contiguous():
+                raise RuntimeError(f"{what} must be a contiguous CUDA {desc.weight_dtype} tensor of shape {shape}, "
+                                   f"got {tuple(t.shape)} {t.dtype}")
         dev = desc.device
         H, D, T = desc.head_num, self.size_per_head, desc.max_full_seq_len
         # per-layer caches, [batch][head][time][dim] so that one (batch, head) history is contiguous
@@ -394,7 +414,7 @@ class _MmhaBase:
         out = _pool.get("self_mask_attn_cache", d.batch_size * d.max_seq_len * d.hidden_units, torch.float16, d.device)
         out = out[: B * S * d.hidden_units].view(B * S, d.hidden_units)
         inp2d = inp.reshape(B * S, d.hidden_units)
-        if _defer[0] and B * S <= _DECODE_MAX_M:
+        if _defer[0] and B * S <= _DECODE_MAX_M and d.is_int8:
             peer = None
             if d.tp is not None and d.tp.size > 1:
                 # row-parallel: the ranks' fp32 partial sums are added before scale, residual and rounding -
@@ -407,9 +427,9 @@ class _MmhaBase:
             gemm_w8a16_accum(ctx2d, self.out_w, sums)
             _pending[out.data_ptr()] = _Pending(sums, self.out_s, inp2d, out, peer)
         elif d.tp is None or d.tp.size == 1:
-            gemm_w8a16(ctx2d, self.out_w, self.out_s, out=out, residual=inp2d)
+            _linear(ctx2d, self.out_w, self.out_s, out, residual=inp2d)
         else:
-            gemm_w8a16(ctx2d, self.out_w, self.out_s, out=out)
+            _linear(ctx2d, self.out_w, self.out_s, out)
             d.tp.all_reduce(out)
             check(lib.eet_add_residual(out.data_ptr(), inp2d.data_ptr(), out.numel(), _stream()))
         return out.view(B, S, d.hidden_units)
@@ -448,7 +468,7 @@ class _MmhaBase:
         _norm_head(inp.view(M, h), self.ln_w, d.layernorm_eps, xn)
         qkv = _pool.get("qkv_full", cap * 3 * self.inner_dim, torch.float16, d.device)[: M * 3 * self.inner_dim]
         qkv = qkv.view(M, 3 * self.inner_dim)
-        gemm_w8a16(xn, self.qkv_w, self.qkv_s, out=qkv)
+        _linear(xn, self.qkv_w, self.qkv_s, qkv)
         q = _pool.get("q_buf", cap * self.inner_dim, torch.float16, d.device)[: M * self.inner_dim]
         check(lib.eet_qkv_split_store(qkv.data_ptr(), q.data_ptr(), self.k_cache.data_ptr(), self.v_cache.data_ptr(),
                                       B, S, H, D, d.max_full_seq_len, int(self.ROPE), self.rope_base, _stream()))
@@ -478,7 +498,7 @@ class _MmhaBase:
         xn = _pool.get("layernorm_inc", d.batch_size * h, torch.float16, d.device)[: B * h].view(B, h)
         _norm_head(inp.view(B, h), self.ln_w, d.layernorm_eps, xn)
         qkv, qkv_sums = None, None
-        if _defer[0] and B <= _DECODE_MAX_M:
+        if _defer[0] and B <= _DECODE_MAX_M and d.is_int8:
             # the attention kernel finishes the projection itself: fp16(sums * scale)
             qkv_sums = _pool.zeros("qkv_sums", d.batch_size * 3 * self.inner_dim, torch.float32, d.device)
             qkv_sums = qkv_sums[: B * 3 * self.inner_dim].view(B, 3 * self.inner_dim)
@@ -486,7 +506,7 @@ class _MmhaBase:
         else:
             qkv = _pool.get("qkv_inc", d.batch_size * 3 * self.inner_dim, torch.float16, d.device)
             qkv = qkv[: B * 3 * self.inner_dim].view(B, 3 * self.inner_dim)
-            gemm_w8a16(xn, self.qkv_w, self.qkv_s, out=qkv)
+            _linear(xn, self.qkv_w, self.qkv_s, qkv)
         if reorder_state is not None and reorder_state.numel() != 0:
             self._reorder(reorder_state, B)
         ctx = _pool.get("context_buf", d.batch_size * self.inner_dim, torch.float16, d.device)[: B * self.inner_dim]
@@ -503,7 +523,7 @@ class _MmhaBase:
         step_dev = None
         if self.use_device_step:
             step_dev = self._arena.data_ptr() + 4 * self._slot
-        check(lib.eet_decode_mha(_ptr(qkv), _ptr(qkv_sums), self.qkv_s.data_ptr(), self.k_cache.data_ptr(),
+        check(lib.eet_decode_mha(_ptr(qkv), _ptr(qkv_sums), _ptr(self.qkv_s), self.k_cache.data_ptr(),
                                  self.v_cache.data_ptr(), ctx.data_ptr(),
                                  B, H, D, d.max_full_seq_len, self.step_, step_dev, _ptr(pre_padding_len),
                                  _ptr(alibi), alibi_stride, _ptr(slopes), int(self.ROPE), self.rope_base, 0,
@@ -556,10 +576,12 @@ class GatedFeedForwardNetworkInt8:
     """EET.GatedFeedForwardNetworkInt8 (csrc/py11/eet2py.cpp:126-134, csrc/op/gated_ffn_int8.{hpp,cpp}):
     RMSNorm -> act(x.W0) * (x.W1) -> .W_out (+ residual)."""
 
+    INT8 = True
+
     def __init__(self, desc, Intermediate_0_weights, Intermediate_0_scale, Intermediate_0_bias,
                  Intermediate_1_weights, Intermediate_1_scale, Intermediate_1_bias, Output_weights, Output_scale,
                  Output_bias, layernorm_weights, layernorm_bias, ffn_cache_name="out_cache"):
-        desc._require_int8_half("GatedFeedForwardNetworkInt8")
+        desc._require_half(type(self).__name__, int8=self.INT8)
         if desc.activation_fn != "silu":
             # the reference prints "unsupported activation" for unknown names and supports gelu/relu gates
             # too (gated_ffn_int8.cpp:40-61); the LLaMA/Baichuan path uses silu only
@@ -579,8 +601,9 @@ class GatedFeedForwardNetworkInt8:
         for t, shape, what in ((self.w0, (h, self.d_ff), "Intermediate_0_weights"),
                                (self.w1, (h, self.d_ff), "Intermediate_1_weights"),
                                (self.w_out, (self.d_ff, h), "Output_weights")):
-            if tuple(t.shape) != shape or t.dtype != torch.int8 or not t.is_cuda:
-                raise RuntimeError(f"{what} must be a CUDA int8 tensor of shape {shape}, got {tuple(t.shape)} {t.dtype}")
+            if tuple(t.shape) != shape or t.dtype != desc.weight_dtype or not t.is_cuda or not t.is_contiguous():
+                raise RuntimeError(f"{what} must be a contiguous CUDA {desc.weight_dtype} tensor of shape {shape}, "
+                                   f"got {tuple(t.shape)} {t.dtype}")
 
     def forward(self, input, pre_layernorm=True, add_residual=True):
         d = self.desc
@@ -597,7 +620,7 @@ class GatedFeedForwardNetworkInt8:
             act = _pool.get("ffn_inner_act", cap * self.d_ff, torch.float16, d.device)[: M * self.d_ff].view(M, self.d_ff)
             out = _pool.get(self.cache_name, cap * h, torch.float16, d.device)[: M * h].view(M, h)
             inp2d = input.view(M, h)
-            deferred = _defer[0] and M <= _DECODE_MAX_M
+            deferred = _defer[0] and M <= _DECODE_MAX_M and d.is_int8
             if deferred:
                 # gate and up in one launch, their epilogues inside the SwiGLU kernel
                 gs = _pool.zeros("gate_sums", d.batch_size * self.d_ff, torch.float32, d.device)[: M * self.d_ff].view(M, self.d_ff)
@@ -607,8 +630,8 @@ class GatedFeedForwardNetworkInt8:
                                               act.data_ptr(), M, self.d_ff, _stream()))
             else:
                 lin = _pool.get("ffn_inner_linear", cap * self.d_ff, torch.float16, d.device)[: M * self.d_ff].view(M, self.d_ff)
-                gemm_w8a16(xn, self.w0, self.s0, out=act)
-                gemm_w8a16(xn, self.w1, self.s1, out=lin)
+                _linear(xn, self.w0, self.s0, act)
+                _linear(xn, self.w1, self.s1, lin)
                 check(lib.eet_swiglu(act.data_ptr(), lin.data_ptr(), M, self.d_ff, _stream()))
             if deferred and add_residual:
                 peer = None
@@ -620,15 +643,68 @@ class GatedFeedForwardNetworkInt8:
                 gemm_w8a16_accum(act, self.w_out, sums)
                 _pending[out.data_ptr()] = _Pending(sums, self.s_out, inp2d, out, peer)
             elif d.tp is None or d.tp.size == 1:
-                gemm_w8a16(act, self.w_out, self.s_out, out=out, residual=inp2d if add_residual else None)
+                _linear(act, self.w_out, self.s_out, out, residual=inp2d if add_residual else None)
             else:
-                gemm_w8a16(act, self.w_out, self.s_out, out=out)
+                _linear(act, self.w_out, self.s_out, out)
                 d.tp.all_reduce(out)
                 if add_residual:
                     check(lib.eet_add_residual(out.data_ptr(), inp2d.data_ptr(), out.numel(), _stream()))
         return out.view(B, S, h)
 
     __call__ = forward
+
+
+class GatedFeedForwardNetwork(GatedFeedForwardNetworkInt8):
+    """EET.GatedFeedForwardNetwork (csrc/py11/eet2py.cpp:117-124, csrc/op/gated_ffn.{hpp,cpp}): the fp16 twin
+    the reference builds when data_type is torch.float16 (modeling_llama.py:118-123).  Same flow with fp16
+    weights [in, out] and no scales."""
+
+    INT8 = False
+
+    def __init__(self, desc, Intermediate_0_weights, Intermediate_0_bias, Intermediate_1_weights, Intermediate_1_bias,
+                 Output_weights, Output_bias, layernorm_weights, layernorm_bias, ffn_cache_name="out_cache"):
+        super().__init__(desc, Intermediate_0_weights, None, Intermediate_0_bias, Intermediate_1_weights, None,
+                         Intermediate_1_bias, Output_weights, None, Output_bias, layernorm_weights, layernorm_bias,
+                         ffn_cache_name)
+
+
+# ---------------------------------------------------------------------------------------------------
+# Embedding op
+# ---------------------------------------------------------------------------------------------------
+class Embedding:
+    """EET.Embedding (csrc/py11/eet2py.cpp:136-141, csrc/op/embedding.{hpp,cpp}).  The reference's LLaMA and
+    Baichuan models import this name but look tokens up with torch.nn.Embedding
+    (modeling_llama.py:36,281-283); it is provided so that `from EET import Embedding` keeps working and
+    is plain tensor indexing: word + token-type + position rows (embedding.cpp:105-137), optional
+    LayerNorm with bias (the BERT/GPT form; :83-94)."""
+
+    def __init__(self, desc, embedding_weights, position_weights, token_type_weights, layernorm_weights, layernorm_bias,
+                 emb_cache_name="emb_cache"):
+        self.desc = desc
+        self.word, self.pos, self.tok = embedding_weights, position_weights, token_type_weights
+        self.ln_w, self.ln_b = layernorm_weights, layernorm_bias
+        self.cache_name = emb_cache_name
+
+    def forward_transformers(self, input_ids, position_ids, token_type_ids, if_layernorm):
+        d = self.desc
+        B, S = input_ids.shape
+        if B > d.batch_size or S > d.max_seq_len:
+            raise RuntimeError("Embedding: input exceeds batch_size / max_seq_len of the MetaDesc")
+        out = _pool.get(self.cache_name, d.batch_size * d.max_seq_len * d.hidden_units, d.dtype, d.device)
+        out = out[: B * S * d.hidden_units].view(B, S, d.hidden_units)
+        torch.index_select(self.word, 0, input_ids.reshape(-1), out=out.view(B * S, -1))
+        if token_type_ids is not None and token_type_ids.numel() != 0:
+            out += self.tok[token_type_ids].expand(B, S, -1)
+        if position_ids is not None and position_ids.numel() != 0:
+            out += self.pos[position_ids].expand(B, S, -1)
+        if if_layernorm:
+            out.copy_(torch.nn.functional.layer_norm(out.float(), (d.hidden_units,), self.ln_w.float(),
+                                                     None if self.ln_b is None or self.ln_b.numel() == 0
+                                                     else self.ln_b.float(), d.layernorm_eps))
+        return out
+
+    def forward_fairseq(self, *args, **kwargs):
+        raise RuntimeError("Embedding.forward_fairseq: the fairseq sinusoidal form is not part of the LLaMA/Baichuan path")
 
 
 # ---------------------------------------------------------------------------------------------------

@@ -15,6 +15,7 @@ import torch.nn as nn
 from . import EET
 from . import tp as tp_mod
 from .EET import GatedFeedForwardNetworkInt8 as eet_gated_ffn
+from .EET import GatedFeedForwardNetwork as eet_gated_ffn_fp16
 from .EET import LayerNorm as eet_layernorm
 from .EET import LlamaMmha as eet_masked_attention
 from .EET import BaichuanMmha as eet_baichuan_13b_attention
@@ -51,6 +52,11 @@ def convert_name(org_key, model_name="llama"):
     return key
 
 
+def _check_data_type(data_type):
+    if data_type not in (torch.int8, torch.float16):
+        raise RuntimeError("this library serves data_type=torch.int8 (W8A16) and torch.float16 only")
+
+
 def _convert(model_dict, data_type, model_attr, fuse_qkv):
     model_dict = dict(model_dict)
     if fuse_qkv:
@@ -84,16 +90,15 @@ def _convert(model_dict, data_type, model_attr, fuse_qkv):
 
 def convert_llama_weights(model_dict, data_type=torch.int8, model_attr="model"):
     """HF LLaMA state dict -> EET dictionary (modeling_llama.py:739-784).  With data_type=torch.int8 every
-    2-D layer weight becomes `<name>.weight` (packed int8 [K, N]) + `<name>.scale` ([N])."""
-    if data_type != torch.int8:
-        raise RuntimeError("this library serves data_type=torch.int8 only")
+    2-D layer weight becomes `<name>.weight` (packed int8 [K, N]) + `<name>.scale` ([N]); with
+    torch.float16 it is the transposed fp16 matrix [K, N]."""
+    _check_data_type(data_type)
     return _convert(model_dict, data_type, model_attr, fuse_qkv=True)
 
 
 def convert_baichuan_weights(model_dict, data_type=torch.int8, model_attr="model"):
     """HF Baichuan state dict (fused W_pack) -> EET dictionary (modeling_baichuan.py:572-603)."""
-    if data_type != torch.int8:
-        raise RuntimeError("this library serves data_type=torch.int8 only")
+    _check_data_type(data_type)
     return _convert(model_dict, data_type, model_attr, fuse_qkv=False)
 
 
@@ -123,6 +128,8 @@ def _shard_cols(packed, scale, tp, lo, hi, blocks=1):
     if tp is None or tp.size == 1:
         return packed, scale
     K, N = packed.shape
+    if packed.dtype != torch.int8:   # fp16 twin: plain [K, N] matrix, no scale
+        return packed.view(K, blocks, N // blocks)[:, :, lo:hi].reshape(K, -1).contiguous(), scale
     q = EET.unpack_weights(packed).view(K, blocks, N // blocks)
     s = scale.view(blocks, N // blocks)
     return EET.preprocess_weights(q[:, :, lo:hi].reshape(K, -1).contiguous()), s[:, lo:hi].reshape(-1).contiguous()
@@ -133,6 +140,8 @@ def _shard_rows(packed, scale, tp, lo, hi):
     and are replicated); the rank keeps rows [lo, hi) of K."""
     if tp is None or tp.size == 1:
         return packed, scale
+    if packed.dtype != torch.int8:
+        return packed[lo:hi].contiguous(), scale
     q = EET.unpack_weights(packed)
     return EET.preprocess_weights(q[lo:hi].contiguous()), scale
 
@@ -141,7 +150,11 @@ class _DecoderLayer:
     """EETLlamaDecoderLayer / EETBaichuanDecoderLayer (modeling_llama.py:150-199): attention op + FFN op
     and the tensors they point at."""
 
-    def __init__(self, config, model_dict, layer_id, attention_cls):
+    NAMES = ("ln1", "ln2", "qkv_w", "qkv_s", "out_w", "out_s", "w0", "s0", "w1", "s1", "w2", "s2")
+
+    @staticmethod
+    def _tensors(config, model_dict, layer_id):
+        """This rank's tensors of one layer, in NAMES order, from an EET dictionary."""
         dev = config.device
         tp = config.tp
         p = f"layer.{layer_id}."
@@ -149,23 +162,39 @@ class _DecoderLayer:
         def cuda(name):
             return model_dict[p + name].to(dev)
 
-        self.ln1 = cuda("self_attn.layernorm.weight").half()
-        self.ln2 = cuda("ffn.layernorm.weight").half()
+        def scale(name):
+            # the fp16 twin has no scales: the reference passes torch.empty(0) (modeling_llama.py:63-64)
+            return cuda(name).half() if config.is_int8 else _EMPTY
+
         a_lo, a_hi = config.shard_attn   # inner-dim columns of this rank inside each of Q, K, V
         f_lo, f_hi = config.shard_ffn    # d_ff channels of this rank
-        self.qkv_w, self.qkv_s = _shard_cols(cuda("self_attn.qkv_proj.weight"), cuda("self_attn.qkv_proj.scale").half(),
-                                             tp, a_lo, a_hi, 3)
-        self.out_w, self.out_s = _shard_rows(cuda("self_attn.out_proj.weight"), cuda("self_attn.out_proj.scale").half(),
-                                             tp, a_lo, a_hi)
-        self.w0, self.s0 = _shard_cols(cuda("ffn.intermediate_0.weight"), cuda("ffn.intermediate_0.scale").half(),
-                                       tp, f_lo, f_hi)
-        self.w1, self.s1 = _shard_cols(cuda("ffn.intermediate_1.weight"), cuda("ffn.intermediate_1.scale").half(),
-                                       tp, f_lo, f_hi)
-        self.w2, self.s2 = _shard_rows(cuda("ffn.output.weight"), cuda("ffn.output.scale").half(), tp, f_lo, f_hi)
+        qkv_w, qkv_s = _shard_cols(cuda("self_attn.qkv_proj.weight"), scale("self_attn.qkv_proj.scale"), tp, a_lo, a_hi, 3)
+        out_w, out_s = _shard_rows(cuda("self_attn.out_proj.weight"), scale("self_attn.out_proj.scale"), tp, a_lo, a_hi)
+        w0, s0 = _shard_cols(cuda("ffn.intermediate_0.weight"), scale("ffn.intermediate_0.scale"), tp, f_lo, f_hi)
+        w1, s1 = _shard_cols(cuda("ffn.intermediate_1.weight"), scale("ffn.intermediate_1.scale"), tp, f_lo, f_hi)
+        w2, s2 = _shard_rows(cuda("ffn.output.weight"), scale("ffn.output.scale"), tp, f_lo, f_hi)
+        return (cuda("self_attn.layernorm.weight").half(), cuda("ffn.layernorm.weight").half(), qkv_w, qkv_s, out_w,
+                out_s, w0, s0, w1, s1, w2, s2)
+
+    def __init__(self, config, model_dict, layer_id, attention_cls):
+        for name, t in zip(self.NAMES, self._tensors(config, model_dict, layer_id)):
+            setattr(self, name, t)
+        self.config = config
         self.attention = attention_cls(config, self.qkv_w, self.qkv_s, _EMPTY, _EMPTY, _EMPTY, self.out_w, self.out_s,
                                        _EMPTY, self.ln1, _EMPTY)
-        self.feedforward = eet_gated_ffn(config, self.w0, self.s0, _EMPTY, self.w1, self.s1, _EMPTY, self.w2, self.s2,
-                                         _EMPTY, self.ln2, _EMPTY, "decoder_out_cache")
+        if config.is_int8:
+            self.feedforward = eet_gated_ffn(config, self.w0, self.s0, _EMPTY, self.w1, self.s1, _EMPTY, self.w2,
+                                             self.s2, _EMPTY, self.ln2, _EMPTY, "decoder_out_cache")
+        else:
+            self.feedforward = eet_gated_ffn_fp16(config, self.w0, _EMPTY, self.w1, _EMPTY, self.w2, _EMPTY, self.ln2,
+                                                  _EMPTY, "decoder_out_cache")
+
+    def update(self, model_dict, layer_id):
+        """New weights into the tensors the ops (and any captured CUDA graph) already point at: the in-place
+        `.copy_()` of EETLlamaSelfMaskedAttention.update / EETGatedFeedForward.update
+        (modeling_llama.py:80-93,133-149)."""
+        for name, t in zip(self.NAMES, self._tensors(self.config, model_dict, layer_id)):
+            getattr(self, name).copy_(t)
 
     def __call__(self, hidden_states, first_pass=True, pre_padding_len=_EMPTY, reorder_state=_EMPTY,
                  relative_attention_bias=_EMPTY):
@@ -192,9 +221,9 @@ class _ModelBase:
     @classmethod
     def from_eet(cls, model_dict, cfg, max_batch, max_prompt_seq_len, max_full_seq_len, data_type=torch.int8,
                  device_id=0, tp=None):
-        """Same arguments as the reference (modeling_llama.py:330-377) plus `tp`."""
-        if data_type != torch.int8:
-            raise RuntimeError("this library serves data_type=torch.int8 only")
+        """Same arguments as the reference (modeling_llama.py:330-377) plus `tp`.  data_type torch.int8
+        builds the W8A16 ops, torch.float16 the fp16 twins (:336-337)."""
+        _check_data_type(data_type)
         torch.set_grad_enabled(False)
         size = 1 if tp is None else tp.size
         rank = 0 if tp is None else tp.rank
@@ -207,7 +236,7 @@ class _ModelBase:
                          layer_num=cfg.num_hidden_layers, max_seq_len=max_prompt_seq_len,
                          max_full_seq_len=max_full_seq_len, activation_fn=cfg.hidden_act,
                          d_kv=head_dim, d_ff=f_hi - f_lo, cuda_device=device,
-                         layernorm_eps=cfg.rms_norm_eps, is_int8=True, tp=tp)
+                         layernorm_eps=cfg.rms_norm_eps, is_int8=(data_type == torch.int8), tp=tp)
         desc.shard_attn = (h_lo * head_dim, h_hi * head_dim)
         desc.shard_ffn = (f_lo, f_hi)
         embedding = nn.Embedding(cfg.vocab_size, cfg.hidden_size, getattr(cfg, "pad_token_id", None))
@@ -225,6 +254,14 @@ class _ModelBase:
     @classmethod
     def _attention_class(cls, cfg):
         return eet_masked_attention
+
+    def update(self, model_dict):
+        """Reloads every weight from an EET dictionary of the same architecture, in place
+        (EETLlamaModel.update, modeling_llama.py:299-327)."""
+        self.embedding.weight.copy_(model_dict["embed_tokens.weight"].to(self.embedding.weight))
+        for i, layer in enumerate(self.layers):
+            layer.update(model_dict, i)
+        self.layer_norm.gamma.copy_(model_dict["norm.weight"].to(self.layer_norm.gamma))
 
     def _bias(self, first_pass, seq_len, like):
         return _EMPTY
@@ -312,6 +349,16 @@ class _CausalLMBase:
         conv = convert_baichuan_weights if any("W_pack" in k for k in sd) else convert_llama_weights
         return cls.from_eet(conv(sd, data_type), torch_model.config, max_batch, max_prompt_seq_len, max_full_seq_len,
                             data_type, device_id=device_id, tp=tp)
+
+    def update(self, torch_model):
+        """Takes new weights from a HF model of the same architecture (re-quantizing them when the model is
+        int8) without reallocating anything: EETLlamaForCausalLM.update (modeling_llama.py:518-522)."""
+        data_type = torch.int8 if self.model.desc.is_int8 else torch.float16
+        sd = {k: v.half() if v.is_floating_point() else v for k, v in torch_model.state_dict().items()}
+        conv = convert_baichuan_weights if any("W_pack" in k for k in sd) else convert_llama_weights
+        model_dict = conv(sd, data_type)
+        self.lm_head.weight.copy_(model_dict["lm_head.weight"].to(self.lm_head.weight))
+        self.model.update({k: v for k, v in model_dict.items() if "lm_head" not in k})
 
     def __call__(self, input_ids, first_pass=True, position_ids=None, attention_mask=None, reorder_state=None,
                  labels=None, **kwargs):
@@ -412,6 +459,40 @@ class _CausalLMBase:
         if attention_mask is not None:
             self.model.pre_padding_len = torch.empty(0).long()
         return torch.cat(toks, dim=1)
+
+    @torch.no_grad()
+    def beam_search(self, input_ids, num_beams, max_new_tokens):
+        """Fixed-length beam search in the shape of GenerationMixin_EET.beam_search
+        (python/eet/pipelines/generation.py:1399-1600): the prompt is repeated num_beams times (the model must
+        have been built with max_batch >= B * num_beams), candidates are ranked by the sum of token
+        log-probabilities, and before every step the ops reorder their KV caches with `reorder_state`
+        (:1564-1580; LlamaMmha::forward_inc, csrc/op/llama_mmha.cpp:250-252).  No EOS stop and no length
+        penalty.  Returns (best sequences [B, prompt + max_new_tokens], their scores [B])."""
+        self.end_graph()
+        B, S = input_ids.shape
+        nb = num_beams
+        dev = input_ids.device
+        ids = input_ids.repeat_interleave(nb, 0)
+        scores = torch.zeros(B, nb, device=dev)
+        scores[:, 1:] = -1e9          # the beams start identical: only the first may spawn candidates
+        logits = self(ids, first_pass=True).logits[:, -1]
+        offs = (torch.arange(B, device=dev) * nb).view(B, 1)
+        try:
+            for t in range(max_new_tokens):
+                logp = torch.log_softmax(logits.float(), -1)
+                V = logp.shape[-1]
+                cand = (scores.view(B, nb, 1) + logp.view(B, nb, V)).view(B, nb * V)
+                scores, idx = cand.topk(nb, -1)
+                beam, tok = idx // V, idx % V
+                reorder = (beam + offs).view(-1)
+                ids = torch.cat([ids[reorder], tok.view(-1, 1)], 1)
+                if t + 1 < max_new_tokens:
+                    logits = self(ids[:, -1:].contiguous(), first_pass=False, reorder_state=reorder).logits[:, -1]
+        finally:
+            self.model.reorder_state = torch.empty(0).long()
+        best = scores.argmax(-1)
+        rows = torch.arange(B, device=dev)
+        return ids.view(B, nb, -1)[rows, best], scores[rows, best]
 
 
 class EETLlamaForCausalLM(_CausalLMBase):

@@ -42,6 +42,19 @@ def gemm_w8a16(x: torch.Tensor, q: torch.Tensor, scale: torch.Tensor, exact: boo
     return (x.to(F32) @ dequant(q, scale, exact)).to(F16)
 
 
+def gemm_fp16(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """The fp16 twin of the projection: x [M,K] fp16 times w [K,N] fp16 (cublasGemmEx in
+    csrc/op/llama_mmha.cpp:288-310 with the compute type of csrc/op/meta_desc.hpp:47).  Restated with fp32
+    accumulation and one fp16 rounding; the reference accumulates in fp16, whose extra error the tests'
+    tolerance covers."""
+    return _h(x.float() @ w.float())
+
+
+def linear(x, w, scale, exact=True):
+    """Dispatch used by DecoderOracle: scale None means fp16 weights [K,N]."""
+    return gemm_fp16(x, w) if scale is None else gemm_w8a16(x, w, scale, exact)
+
+
 def gemm_w8a16_fp32(x, q, scale):
     """The tolerance reference: fp32 dequantize-then-matmul computed in float64, returned as float64."""
     return x.double() @ (q.double() * scale.double()[None, :])
@@ -183,8 +196,8 @@ def alibi_mask(n_head: int, max_pos: int) -> torch.Tensor:
 
 # ------------------------------------------------------------------------------------------ blocks
 class LayerWeights:
-    """One decoder layer in un-packed form: row-major int8 [K,N] + fp16 scale [N] per projection, RMSNorm
-    gammas in fp16.  qkv is the fused [h, 3*inner] matrix in Q-block, K-block, V-block column order
+    """One decoder layer in un-packed form: row-major int8 [K,N] + fp16 scale [N] per projection (or fp16
+    [K,N] with scale None for the fp16 twin ops), RMSNorm gammas in fp16.  qkv is the fused [h, 3*inner] matrix in Q-block, K-block, V-block column order
     (python/eet/transformers/modeling_llama.py:745-753)."""
 
     def __init__(self, qkv, qkv_s, out, out_s, gate, gate_s, up, up_s, down, down_s, ln1, ln2):
@@ -212,7 +225,7 @@ class DecoderOracle:
         B, S, h = x.shape
         H, D = self.H, self.D
         xn = rmsnorm(x, L.ln1, self.eps)
-        qkv = gemm_w8a16(xn.reshape(B * S, h), L.qkv, L.qkv_s, self.exact).view(B, S, 3, H, D)
+        qkv = linear(xn.reshape(B * S, h), L.qkv, L.qkv_s, self.exact).view(B, S, 3, H, D)
         q, k, v = (qkv[:, :, i].transpose(1, 2).contiguous() for i in range(3))  # [B,H,S,D]
         if first_pass:
             if self.rope:
@@ -231,18 +244,26 @@ class DecoderOracle:
             ctx = decode_attention(q[:, :, 0], k[:, :, 0], v[:, :, 0], self.kc[li][:B], self.vc[li][:B], step,
                                    pad_len, al).unsqueeze(2)
         ctx = ctx.transpose(1, 2).reshape(B * S, H * D)
-        o = gemm_w8a16(ctx, L.out, L.out_s, self.exact).view(B, S, h)
+        o = linear(ctx, L.out, L.out_s, self.exact).view(B, S, h)
         return add_residual(o, x)   # the residual is always added (llama_mmha.cpp:461-463)
 
     def _ffn_block(self, li, x):
         L = self.layers[li]
         B, S, h = x.shape
         xn = rmsnorm(x, L.ln2, self.eps).reshape(B * S, h)
-        g = gemm_w8a16(xn, L.gate, L.gate_s, self.exact)
-        u = gemm_w8a16(xn, L.up, L.up_s, self.exact)
+        g = linear(xn, L.gate, L.gate_s, self.exact)
+        u = linear(xn, L.up, L.up_s, self.exact)
         a = gated_silu(g, u)
-        o = gemm_w8a16(a, L.down, L.down_s, self.exact).view(B, S, h)
+        o = linear(a, L.down, L.down_s, self.exact).view(B, S, h)
         return add_residual(o, x)
+
+    def reorder(self, index):
+        """Beam search: cache row b takes the history of row index[b] before the step
+        (reorderKV_kernel, csrc/core/transpose.cu:136-162; called first in llama_mmha.cpp:250-252)."""
+        n = len(index)
+        for li in range(len(self.layers)):
+            self.kc[li][:n] = self.kc[li][index].clone()
+            self.vc[li][:n] = self.vc[li][index].clone()
 
     def forward(self, x, first_pass, pad_len=None):
         """x: [B, S, h] fp16.  first_pass resets the step counter to S (llama_mmha.cpp:121,195); every

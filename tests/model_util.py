@@ -47,7 +47,7 @@ def _quant(w_out_in):
     return torch.from_numpy(q), torch.from_numpy(s)
 
 
-def oracle_layers(sd, cfg, fused_qkv=False):
+def oracle_layers(sd, cfg, fused_qkv=False, int8=True):
     layers = []
     for i in range(cfg.num_hidden_layers):
         p = f"model.layers.{i}."
@@ -58,7 +58,7 @@ def oracle_layers(sd, cfg, fused_qkv=False):
         args = []
         for w in (qkv, sd[p + "self_attn.o_proj.weight"], sd[p + "mlp.gate_proj.weight"],
                   sd[p + "mlp.up_proj.weight"], sd[p + "mlp.down_proj.weight"]):
-            args.extend(_quant(w))
+            args.extend(_quant(w) if int8 else (w.t().contiguous(), None))
         layers.append(ops.LayerWeights(*args, sd[p + "input_layernorm.weight"], sd[p + "post_attention_layernorm.weight"]))
     return layers
 
@@ -67,14 +67,44 @@ class OracleLM:
     """Embedding -> DecoderOracle -> final RMSNorm -> lm_head, all on the CPU, mirroring
     EETLlamaForCausalLM.__call__ (python/eet/transformers/modeling_llama.py:262-297,452-491)."""
 
-    def __init__(self, sd, cfg, max_len, batch, rope=True, fused_qkv=False, exact=True):
+    def __init__(self, sd, cfg, max_len, batch, rope=True, fused_qkv=False, exact=True, int8=True):
         self.sd, self.cfg = sd, cfg
-        self.dec = ops.DecoderOracle(oracle_layers(sd, cfg, fused_qkv), cfg.num_attention_heads,
+        self.dec = ops.DecoderOracle(oracle_layers(sd, cfg, fused_qkv, int8), cfg.num_attention_heads,
                                      cfg.hidden_size // cfg.num_attention_heads, cfg.rms_norm_eps, max_len, batch,
                                      rope=rope, exact=exact)
 
-    def __call__(self, ids, first_pass, pad_len=None):
+    def __call__(self, ids, first_pass, pad_len=None, reorder=None):
+        if reorder is not None:
+            self.dec.reorder(reorder)
         x = self.sd["model.embed_tokens.weight"][ids]
         x = self.dec.forward(x, first_pass, pad_len)
         x = ops.rmsnorm(x, self.sd["model.norm.weight"], self.cfg.rms_norm_eps)
         return (x.float() @ self.sd["lm_head.weight"].float().t())
+
+
+def oracle_beam_search(lm, prompt, num_beams, new_tokens):
+    """Fixed-length beam search over an OracleLM (sum of log-probabilities, no length penalty, no EOS): the
+    algorithm of eet_b200.modeling.beam_search restated on the CPU.  Returns (sequences [B, S+new], scores [B],
+    margins): margins[t] is the smallest gap between the last kept and the first dropped candidate at step t,
+    so a test can tell a real disagreement from a near tie."""
+    B, S = prompt.shape
+    nb = num_beams
+    ids = prompt.repeat_interleave(nb, 0)
+    scores = torch.zeros(B, nb)
+    scores[:, 1:] = -1e9
+    logits = lm(ids, True)[:, -1]
+    margins, reorder = [], None
+    for t in range(new_tokens):
+        if t > 0:
+            logits = lm(ids[:, -1:], False, reorder=reorder)[:, -1]
+        logp = torch.log_softmax(logits.float(), -1)
+        V = logp.shape[-1]
+        cand = (scores.view(B, nb, 1) + logp.view(B, nb, V)).view(B, nb * V)
+        top = cand.topk(nb + 1, -1)
+        margins.append(float((top.values[:, :-1] - top.values[:, 1:]).min()))
+        scores, idx = top.values[:, :nb], top.indices[:, :nb]
+        beam, tok = idx // V, idx % V
+        reorder = (beam + torch.arange(B).view(B, 1) * nb).view(-1)
+        ids = torch.cat([ids[reorder], tok.view(-1, 1)], 1)
+    best = scores.argmax(-1)
+    return ids.view(B, nb, -1)[torch.arange(B), best], scores[torch.arange(B), best], margins

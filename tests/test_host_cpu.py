@@ -57,3 +57,31 @@ def test_shard_plan():
 def test_alibi_mask_shape():
     m = gen_alibi_mask(8, 5)
     assert m.shape == (8, 5, 5) and torch.isinf(m[0, 0, 1]) and m[0, 4, 0] == 0
+
+
+def test_every_name_the_reference_models_import_exists():
+    """The import lines of python/eet/transformers/modeling_llama.py:35-42, modeling_baichuan.py:34-42 and
+    encoder_decoder.py:22 must keep working against this module."""
+    import sys
+    import eet_b200
+    eet_b200.install_as_EET()
+    try:
+        from EET import MetaDesc, Embedding, GatedFeedForwardNetworkInt8, GatedFeedForwardNetwork  # noqa: F401
+        from EET import LlamaMmha, BaichuanMmha, LayerNorm, preprocess_weights, quant_weights      # noqa: F401
+    finally:
+        sys.modules.pop("EET", None)
+
+
+def test_convert_weights_data_types():
+    from eet_b200 import modeling
+    with pytest.raises(RuntimeError):
+        modeling.convert_llama_weights({}, torch.float32)
+    w = {"model.layers.0.mlp.down_proj.weight": torch.randn(8, 16).half(),
+         "model.layers.0.self_attn.q_proj.weight": torch.randn(8, 8).half(),
+         "model.layers.0.self_attn.k_proj.weight": torch.randn(8, 8).half(),
+         "model.layers.0.self_attn.v_proj.weight": torch.randn(8, 8).half()}
+    d = modeling.convert_llama_weights(w, torch.float16)
+    # [K = in, N = out] like the reference's fp branch (modeling_llama.py:773-782); no scales
+    assert d["layer.0.ffn.output.weight"].shape == (16, 8) and d["layer.0.ffn.output.weight"].dtype == torch.float16
+    assert d["layer.0.self_attn.qkv_proj.weight"].shape == (8, 24)
+    assert not any(k.endswith(".scale") for k in d)

@@ -103,3 +103,86 @@ def test_beam_reorder_state_moves_the_cache():
     same_tok = ids[1:2, S:S + 1].expand(B, 1).contiguous()
     out = model(same_tok.cuda(), first_pass=False, reorder_state=torch.tensor([1, 1]).cuda()).logits.cpu()
     assert torch.allclose(out[0].float(), out[1].float(), atol=1e-3, rtol=1e-3)
+
+
+def test_beam_search_matches_oracle():
+    from model_util import oracle_beam_search
+    cfg = tiny_config()
+    sd = random_hf_state_dict(cfg, seed=9)
+    B, S, NB, NEW, T = 2, 4, 3, 5, 12
+    model = _build(cfg, sd, "EETLlamaForCausalLM", "convert_llama_weights", B * NB, 8, T)
+    gen = torch.Generator().manual_seed(10)
+    prompt = torch.randint(0, cfg.vocab_size, (B, S), generator=gen)
+    seqs, scores = model.beam_search(prompt.cuda(), NB, NEW)
+    assert seqs.shape == (B, S + NEW) and torch.equal(seqs[:, :S].cpu(), prompt)
+    want_seqs, want_scores, margins = oracle_beam_search(OracleLM(sd, cfg, max_len=T, batch=B * NB), prompt, NB, NEW)
+    # log-probabilities carry the logits' tolerance; the beams themselves must agree unless some step of the
+    # oracle was a near tie between a kept and a dropped candidate
+    assert torch.allclose(scores.cpu(), want_scores, atol=0.1)
+    if min(margins) > 5e-2:
+        assert torch.equal(seqs.cpu(), want_seqs)
+    # greedy generation afterwards is unaffected by the beam state
+    assert model.model.reorder_state.numel() == 0
+
+
+def test_fp16_twin_ops_match_oracle():
+    """data_type=torch.float16: GatedFeedForwardNetwork and the fp16 branch of LlamaMmha
+    (python/eet/transformers/modeling_llama.py:118-123,336-337)."""
+    from eet_b200 import EET, modeling
+    cfg = tiny_config()
+    sd = random_hf_state_dict(cfg, seed=11)
+    B, S, T = 2, 6, 12
+    eet_dict = modeling.convert_llama_weights({k: v.clone() for k, v in sd.items()}, torch.float16)
+    assert eet_dict["layer.0.self_attn.qkv_proj.weight"].dtype == torch.float16
+    assert "layer.0.self_attn.qkv_proj.scale" not in eet_dict
+    model = modeling.EETLlamaForCausalLM.from_eet(eet_dict, cfg, B, 8, T, torch.float16)
+    assert isinstance(model.model.layers[0].feedforward, EET.GatedFeedForwardNetwork)
+    lm = OracleLM(sd, cfg, max_len=T, batch=B, int8=False)
+    gen = torch.Generator().manual_seed(12)
+    ids = torch.randint(0, cfg.vocab_size, (B, S + 3), generator=gen)
+    assert _logits_close(model(ids[:, :S].cuda(), first_pass=True).logits, lm(ids[:, :S], True))
+    for t in range(S, S + 3):
+        assert _logits_close(model(ids[:, t:t + 1].cuda(), first_pass=False).logits, lm(ids[:, t:t + 1], False))
+    toks = model.generate(ids[:, :S].cuda(), 3)
+    assert toks.shape == (B, S + 3)
+
+
+def test_update_requantizes_in_place_and_keeps_the_graph():
+    """EETLlamaForCausalLM.update (python/eet/transformers/modeling_llama.py:518-522): new weights go into
+    the tensors the ops already hold."""
+    import types
+    cfg = tiny_config()
+    sd_a, sd_b = random_hf_state_dict(cfg, seed=13), random_hf_state_dict(cfg, seed=14)
+    B, S, T = 2, 5, 12
+    model = _build(cfg, sd_a, "EETLlamaForCausalLM", "convert_llama_weights", B, 8, T)
+    ptr = model.model.layers[0].qkv_w.data_ptr()
+    gen = torch.Generator().manual_seed(15)
+    ids = torch.randint(0, cfg.vocab_size, (B, S), generator=gen)
+    model.use_cuda_graph = True
+    model.generate(ids.cuda(), 4)          # captures the decode graph on the old weights
+    hf_like = types.SimpleNamespace(state_dict=lambda: sd_b, config=cfg)
+    model.update(hf_like)
+    assert model.model.layers[0].qkv_w.data_ptr() == ptr
+    lm = OracleLM(sd_b, cfg, max_len=T, batch=B)
+    assert _logits_close(model(ids.cuda(), first_pass=True).logits, lm(ids, True))
+    graphed = model.generate(ids.cuda(), 4).cpu()
+    model.use_cuda_graph = False
+    assert torch.equal(graphed, model.generate(ids.cuda(), 4).cpu())
+
+
+def test_embedding_op():
+    from eet_b200 import EET
+    B, S, h, V = 2, 5, 64, 50
+    desc = EET.MetaDesc(torch.float16, B, 2, h, 1, 8, 16, "silu", cuda_device="cuda:0")
+    gen = torch.Generator().manual_seed(16)
+    word, pos, tok = (torch.randn(n, h, generator=gen).half().cuda() for n in (V, 16, 2))
+    emb = EET.Embedding(desc, word, pos, tok, torch.ones(h).half().cuda(), torch.zeros(h).half().cuda(), "emb_cache")
+    ids = torch.randint(0, V, (B, S), generator=gen).cuda()
+    pid = torch.arange(S).view(1, S).cuda()
+    tid = torch.zeros(B, S, dtype=torch.long).cuda()
+    got = emb.forward_transformers(ids, pid, tid, False)
+    want = ((word[ids] + tok[tid]) + pos[pid]).half()
+    assert got.shape == (B, S, h) and torch.equal(got, want)
+    normed = emb.forward_transformers(ids, pid, tid, True)
+    ref = torch.nn.functional.layer_norm(want.float(), (h,), eps=desc.layernorm_eps).half()
+    assert torch.allclose(normed.float(), ref.float(), atol=2e-3)
