@@ -38,6 +38,32 @@ UNIT = "tokens/s"
 CFG = dict(hidden_size=4096, num_attention_heads=32, num_hidden_layers=32, intermediate_size=11008, vocab_size=32000,
            rms_norm_eps=1e-6, hidden_act="silu", pad_token_id=None)
 BATCH, PROMPT = 8, 512
+WORKLOAD, FAMILY = "llama7b_arch_int8_decode_b8_prompt512", "llama"
+
+# The headline configuration above is what a run without --workload measures.  The two other model-level
+# configurations of the reference's latency scripts are selectable for additional lines:
+WORKLOADS = {
+    "llama7b": None,
+    # Baichuan-13B architecture (ALiBi attention op), batch 32, prompt 256
+    "baichuan13b": dict(metric="int8_baichuan13b_decode_tokens_per_s", workload="baichuan13b_arch_int8_decode_b32_prompt256",
+                        family="baichuan", batch=32, prompt=256,
+                        cfg=dict(hidden_size=5120, num_attention_heads=40, num_hidden_layers=40, intermediate_size=13696,
+                                 vocab_size=64000)),
+    # LLaMA-65B architecture, batch 64, prompt 1024: weights + KV cache need at least two GPUs
+    "llama65b": dict(metric="int8_llama65b_decode_tokens_per_s", workload="llama65b_arch_int8_decode_b64_prompt1024",
+                     family="llama", batch=64, prompt=1024,
+                     cfg=dict(hidden_size=8192, num_attention_heads=64, num_hidden_layers=80, intermediate_size=22016,
+                              vocab_size=32000)),
+}
+
+
+def select_workload(name):
+    global METRIC, BATCH, PROMPT, WORKLOAD, FAMILY
+    w = WORKLOADS[name]
+    if w is None:
+        return
+    METRIC, WORKLOAD, FAMILY, BATCH, PROMPT = w["metric"], w["workload"], w["family"], w["batch"], w["prompt"]
+    CFG.update(w["cfg"])
 
 
 def peaks():
@@ -100,7 +126,7 @@ class ClockSampler:
 
 # ------------------------------------------------------------------------------------------------ model
 def build_model(tp, device_index, t_max, layers=None):
-    """Random-init LLaMA-7B-architecture weights (N(0, 0.02^2), fp16) generated on the GPU, quantized by the
+    """Random-init weights of the selected architecture (N(0, 0.02^2), fp16) generated on the GPU, quantized by the
     library's quantizer, and assembled through the public from_eet() entry point.  Every rank draws the same
     full matrices (same seed) and keeps its shard."""
     from eet_b200 import EET, modeling
@@ -125,8 +151,8 @@ def build_model(tp, device_index, t_max, layers=None):
             d[p + name + ".weight"], d[p + name + ".scale"] = qw(k, n)
         d[p + "self_attn.layernorm.weight"] = torch.ones(h, device=dev).half()
         d[p + "ffn.layernorm.weight"] = torch.ones(h, device=dev).half()
-    model = modeling.EETLlamaForCausalLM.from_eet(d, cfg, BATCH, PROMPT, t_max, torch.int8, device_id=device_index,
-                                                  tp=tp)
+    cls = modeling.EETBaichuanForCausalLM if FAMILY == "baichuan" else modeling.EETLlamaForCausalLM
+    model = cls.from_eet(d, cfg, BATCH, PROMPT, t_max, torch.int8, device_id=device_index, tp=tp)
     return model, cfg
 
 
@@ -379,14 +405,15 @@ def run_ours(args):
     dom = gemms["qkv"]   # the largest single launch of a layer: fused QKV projection
     # dram__bytes_read.sum + dram__bytes_write.sum of one such launch at TP 1 (K=4096, N=12288, M=8), from the
     # ncu capture summarised in profiles/gemm_skinny_m8_llama7b_shapes.md; scaled by the bytes of the shard
-    traffic = 50.81e6 * dom["bytes"] / 50620416.0
+    # (no capture exists for the other workloads' shapes: traffic is reported as null there)
+    traffic = 50.81e6 * dom["bytes"] / 50620416.0 if WORKLOAD.startswith("llama7b") else None
     line = {"metric": METRIC, "value": round(BATCH * K / t_dev, 2), "unit": UNIT, "n_gpus": world, "steps": K,
             "warmup": W, "ms_per_step": round(t_dev / K * 1e3, 4), "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "f16 activations x int8 weights, f32 accumulate", "data": "synthetic",
-            "config": {"workload": "llama7b_arch_int8_decode_b8_prompt512", "layers": n_layers, "global_batch": BATCH,
+            "config": {"workload": WORKLOAD, "layers": n_layers, "global_batch": BATCH,
                        "seq_len": PROMPT, "cache_len_during_timing": [PROMPT + W + 1, PROMPT + W + K],
                        "parallelism": f"tp{world}", "cuda_graph": model.use_cuda_graph,
-                       "l2": "weights (6.5 GB per step) and KV cache exceed L2; no flush needed"},
+                       "l2": "weights (GBs per step) and KV cache exceed L2; no flush needed"},
             "e2e": {"value": round(BATCH * K / t_e2e, 2), "unit": UNIT, "h2d_bytes_per_step": BATCH * 8,
                     "d2h_bytes_per_step": BATCH * 8, "ms_per_step": round(t_e2e / K * 1e3, 4)},
             "prefill": None if prefill_ms is None else {"ms": round(prefill_ms, 2), "tokens": BATCH * PROMPT,
@@ -394,10 +421,11 @@ def run_ours(args):
             "gpu_launches": kernel_launches_per_step(n_layers) * K,
             "clocks": clk.summary(), "clocks_e2e": clk_e2e.summary(), "device_status": status,
             "roofline": {"bound": "hbm",
-                         "kernel": f"gemm_skinny_kernel<1>, fused QKV projection K={dom['K']} N={dom['N']} M={BATCH}",
+                         "kernel": f"gemm_skinny_kernel<{1 if BATCH <= 8 else 2}>, fused QKV projection "
+                                   f"K={dom['K']} N={dom['N']} M={BATCH}",
                          "achieved": round(dom["gbs"], 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                          "frac": round(dom["gbs"] / pk["hbm_gbs"], 4), "peak_source": pk["source"],
-                         "traffic": round(traffic), "algorithmic_bytes": dom["bytes"],
+                         "traffic": None if traffic is None else round(traffic), "algorithmic_bytes": dom["bytes"],
                          "launch_us": round(dom["us"], 2),
                          "all_gemm_launches_of_a_layer": {"achieved": round(g_bytes / g_time / 1e9, 1),
                                                           "frac": round(g_bytes / g_time / 1e9 / pk["hbm_gbs"], 4)},
@@ -431,13 +459,16 @@ def main():
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--layers", type=int, default=None, help="fewer layers than 32 (profiling runs only)")
+    ap.add_argument("--workload", default="llama7b", choices=sorted(WORKLOADS),
+                    help="model-level configuration; the default is the headline one")
+    ap.add_argument("--layers", type=int, default=None, help="fewer layers than the architecture has (profiling runs only)")
     ap.add_argument("--no-graph", action="store_true", help="launch the decode step eagerly")
     ap.add_argument("--no-sweep", action="store_true", help="skip the GEMM sweep")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline")
     ap.add_argument("--skip-prefill", action="store_true",
                     help="fill the KV cache with random data instead of running the prompt (profiling runs only)")
     args = ap.parse_args()
+    select_workload(args.workload)
     if args.warmup < 3:
         args.warmup = 3
     if args.impl == "reference":

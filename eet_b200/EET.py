@@ -255,11 +255,20 @@ class _Pending:
 
 _pending = {}
 _defer = [False]
-_DECODE_MAX_M = 16
+_DECODE_MAX_M = 64       # below the tensor-core GEMM's first M
+_DECODE_MAX_M_TP = 16    # rows of the tensor-parallel peer buffers (tp.PeerBuffers.ROWS)
+
+
+def _defer_ok(M, desc):
+    """Whether an op called with M rows may leave its last projection unfinished for the next op."""
+    if not (_defer[0] and desc.is_int8):
+        return False
+    tp = desc.tp
+    return M <= (_DECODE_MAX_M_TP if tp is not None and tp.size > 1 else _DECODE_MAX_M)
 
 
 class deferred_epilogue:
-    """Context manager for a chain of decode-step ops of this module (M <= 16): inside
+    """Context manager for a chain of decode-step ops of this module (M <= 64; 16 with tensor parallelism): inside
     it an attention / FFN op returns its output tensor *before* the last GEMM's epilogue has run, and the next
     op (attention, FFN or LayerNorm of this module) completes it in its RMSNorm kernel.  Outputs still
     unfinished when the context ends are completed then, so callers outside never see stale memory."""
@@ -414,7 +423,7 @@ class _MmhaBase:
         out = _pool.get("self_mask_attn_cache", d.batch_size * d.max_seq_len * d.hidden_units, torch.float16, d.device)
         out = out[: B * S * d.hidden_units].view(B * S, d.hidden_units)
         inp2d = inp.reshape(B * S, d.hidden_units)
-        if _defer[0] and B * S <= _DECODE_MAX_M and d.is_int8:
+        if _defer_ok(B * S, d):
             peer = None
             if d.tp is not None and d.tp.size > 1:
                 # row-parallel: the ranks' fp32 partial sums are added before scale, residual and rounding -
@@ -498,7 +507,7 @@ class _MmhaBase:
         xn = _pool.get("layernorm_inc", d.batch_size * h, torch.float16, d.device)[: B * h].view(B, h)
         _norm_head(inp.view(B, h), self.ln_w, d.layernorm_eps, xn)
         qkv, qkv_sums = None, None
-        if _defer[0] and B <= _DECODE_MAX_M and d.is_int8:
+        if _defer_ok(B, d):
             # the attention kernel finishes the projection itself: fp16(sums * scale)
             qkv_sums = _pool.zeros("qkv_sums", d.batch_size * 3 * self.inner_dim, torch.float32, d.device)
             qkv_sums = qkv_sums[: B * 3 * self.inner_dim].view(B, 3 * self.inner_dim)
@@ -620,7 +629,7 @@ class GatedFeedForwardNetworkInt8:
             act = _pool.get("ffn_inner_act", cap * self.d_ff, torch.float16, d.device)[: M * self.d_ff].view(M, self.d_ff)
             out = _pool.get(self.cache_name, cap * h, torch.float16, d.device)[: M * h].view(M, h)
             inp2d = input.view(M, h)
-            deferred = _defer[0] and M <= _DECODE_MAX_M and d.is_int8
+            deferred = _defer_ok(M, d)
             if deferred:
                 # gate and up in one launch, their epilogues inside the SwiGLU kernel
                 gs = _pool.zeros("gate_sums", d.batch_size * self.d_ff, torch.float32, d.device)[: M * self.d_ff].view(M, self.d_ff)

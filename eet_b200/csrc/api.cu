@@ -47,6 +47,7 @@ static inline bool aligned16(const void* p)
 #include "attention.cu"
 #include "gemm_skinny.cu"
 #include "gemm_tc.cu"
+#include "gemm_mid.cu"
 #include "glue.cu"
 #include "noalloc.cu"
 #include "quantize.cu"
@@ -129,11 +130,30 @@ int eet_repack_ref_w8(const void* ref_packed, int K, int N, void* packed, void* 
 
 static const int kSkinnyGroupRows = 128;  // rows finished per accumulate + finalize pair when M is large
 
+// Largest M that eet_gemm_w8a16 gives to the stream-K kernel; above it the large-tile kernels take over.
+static int mid_use_max_m()
+{
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("EET_MID_MAX_M");
+        v = e ? atoi(e) : 256;
+        if (v > kMidMaxM) v = kMidMaxM;
+    }
+    return v;
+}
+
 size_t eet_gemm_w8a16_workspace_bytes(int M, int N, int K)
 {
     (void)K;
     if (N <= 0 || M <= 0) return 0;
-    return skinny_sum_bytes(M < kSkinnyGroupRows ? M : kSkinnyGroupRows, N);
+    return skinny_sum_bytes(M <= kMidMaxM ? M : kSkinnyGroupRows, N);
+}
+
+// sums += A x q(B) for any M: the decode kernel up to 16 rows, the stream-K tensor-core kernel above
+static int launch_gemm_accum(const GemmArgs& a, cudaStream_t stream)
+{
+    if (gemm_mid_supported(a.M, a.N, a.K)) return launch_gemm_mid(a, stream);
+    return launch_gemm_skinny(a, stream);
 }
 
 static int check_gemm(const char* who, const void* A, const void* B, int M, int N, int K)
@@ -162,7 +182,7 @@ int eet_gemm_w8a16_accum(const void* A, const void* packedB, float* sums, int M,
     a.M = M;
     a.N = N;
     a.K = K;
-    return launch_gemm_skinny(a, (cudaStream_t)stream);
+    return launch_gemm_accum(a, (cudaStream_t)stream);
 }
 
 int eet_gemm_w8a16_finalize(float* sums, const void* scale, const void* residual, void* C, int M, int N, void* stream)
@@ -184,6 +204,20 @@ int eet_gemm_w8a16(const void* A, const void* packedB, const void* scale, void* 
     EET_CHECK(epilogue == 0 || epilogue == 1, "eet_gemm_w8a16: unknown epilogue %d", epilogue);
     EET_CHECK(epilogue != 1 || residual != nullptr, "eet_gemm_w8a16: epilogue 1 needs a residual");
     const __half* res = epilogue == 1 ? (const __half*)residual : nullptr;
+    if (M <= mid_use_max_m() && gemm_mid_supported(M, N, K)) {
+        // stream-K tensor-core kernel into the fp32 scratch, then one epilogue pass over all rows
+        EET_CHECK(ws && aligned16(ws) && ws_bytes >= skinny_sum_bytes(M, N),
+                  "eet_gemm_w8a16: workspace of %zu bytes is smaller than the %zu needed", ws_bytes, skinny_sum_bytes(M, N));
+        GemmArgs a = {};
+        a.A = (const __half*)A;
+        a.B = (const uint8_t*)packedB;
+        a.ws = (float*)ws;
+        a.M = M;
+        a.N = N;
+        a.K = K;
+        if (int rc = launch_gemm_mid(a, (cudaStream_t)stream)) return rc;
+        return launch_finalize((float*)ws, (const __half*)scale, res, (__half*)C, M, N, (cudaStream_t)stream);
+    }
     if (gemm_tc_supported(M, N, K)) {
         // prefill regime: tcgen05 tensor-core kernel, epilogue fused, no scratch
         return launch_gemm_tc((const __half*)A, (const uint8_t*)packedB, (const __half*)scale, (__half*)C, res, M, N, K,

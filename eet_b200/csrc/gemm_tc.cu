@@ -53,9 +53,11 @@ struct TcSmem {
     volatile int abort;
 };
 
-__device__ __forceinline__ bool tc_wait(uint64_t* bar, uint32_t parity, volatile int* abort)
+// Bounded wait of the warp-specialised kernels.  The roles that issue work are SINGLE threads whose loop
+// is a chain of dependent instructions (a few cycles each at best): the common case - the phase has
+// already completed - must cost one try_wait and nothing else.
+__device__ __noinline__ bool tc_wait_slow(uint64_t* bar, uint32_t parity, volatile int* abort)
 {
-    if (*abort) return false;
     for (uint32_t i = 0; i < kTcSpin; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
         if (*abort) return false;
@@ -63,6 +65,12 @@ __device__ __forceinline__ bool tc_wait(uint64_t* bar, uint32_t parity, volatile
     *abort = 1;
     g_device_status = 2;
     return false;
+}
+
+__device__ __forceinline__ bool tc_wait(uint64_t* bar, uint32_t parity, volatile int* abort)
+{
+    if (mbar_try_wait(bar, parity)) return true;
+    return tc_wait_slow(bar, parity, abort);
 }
 
 // shared-memory matrix descriptor: K-major, 128-byte swizzle, rows of 128 bytes, 8-row groups 1024 B apart

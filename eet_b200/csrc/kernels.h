@@ -33,6 +33,11 @@ bool gemm_tc_supported(int M, int N, int K);
 int launch_gemm_tc(const __half* A, const uint8_t* B, const __half* scale, __half* C, const __half* residual, int M,
                    int N, int K, cudaStream_t stream);
 
+// gemm_mid.cu (stream-K tcgen05, fp32 sums like the skinny kernel)
+constexpr int kMidMaxM = 512;
+bool gemm_mid_supported(int M, int N, int K);
+int launch_gemm_mid(const GemmArgs& a, cudaStream_t stream);
+
 // noalloc.cu
 int gemm_w8a16_noalloc(const __half* A, const uint8_t* B, const __half* scale, __half* C, int M, int N, int K,
                        const __half* residual, cudaStream_t stream);

@@ -171,3 +171,37 @@ def test_baichuan13b_and_llama65b_projection_shapes(KN):
     rows = torch.tensor([0, 1, 63, 64, 127, 128, 255, 256, 300, 383])
     ref = ops.gemm_w8a16_fp32(xl[rows], q, s)
     assert ((y[rows].double() - ref).abs() <= 1e-2 * ref.abs().amax(1, keepdim=True)).all()
+
+
+@pytest.mark.parametrize("M", [17, 32, 40, 64, 100, 128, 250, 256])
+@pytest.mark.parametrize("KN", [(256, 128), (1024, 384), (4096, 4096)])
+def test_stream_k_tensor_core_kernel(KN, M):
+    """16 < M <= 256 goes to the stream-K tcgen05 kernel: token tiles of 32 / 64 / 128 with ragged tails,
+    strips that end inside a CTA's range (small K) and ranges shorter than a strip (large K)."""
+    x, q, s = _case(KN[0], KN[1], M, seed=M + KN[1])
+    _check(_run(x, q, s), x, q, s)
+    res = torch.randn(M, KN[1], generator=torch.Generator().manual_seed(1)).half()
+    y = _run(x, q, s, residual=res)
+    # (two runs may round differently in the last fp16 bit: the order of the fp32 atomic adds is not fixed)
+    assert torch.allclose(y.float(), ops.add_residual(_run(x, q, s), res).float(), rtol=2e-3, atol=2e-3)
+
+
+@pytest.mark.parametrize("M", [24, 64])
+def test_stream_k_accumulate_two_weights_exact_sums(M):
+    """eet_gemm_w8a16_accum above 16 rows, gate and up in one launch: integer-valued inputs make the fp32
+    sums exact, so they must EQUAL the integer product whatever the order of the atomic adds."""
+    from eet_b200 import EET
+    K, N = 512, 640
+    gen = torch.Generator().manual_seed(M)
+    x = torch.randint(-4, 5, (M, K), generator=gen).half()
+    q1 = torch.randint(-128, 128, (K, N), generator=gen, dtype=torch.int8)
+    q2 = torch.randint(-128, 128, (K, N), generator=gen, dtype=torch.int8)
+    sums1 = torch.zeros(M, N, dtype=torch.float32, device="cuda")
+    sums2 = torch.zeros_like(sums1)
+    p1, p2 = EET.preprocess_weights(q1).cuda(), EET.preprocess_weights(q2).cuda()
+    for rep in (1, 2):   # the second launch adds on top of the first
+        EET.gemm_w8a16_accum(x.cuda(), p1, sums1, p2, sums2)
+        assert torch.equal(sums1.cpu().double(), rep * (x.double() @ q1.double()))
+        assert torch.equal(sums2.cpu().double(), rep * (x.double() @ q2.double()))
+    from eet_b200 import _lib
+    assert _lib.device_status() == 0
