@@ -6,22 +6,25 @@
 // (fpA_intB_gemm_template.h:445-495, tile candidates cutlass_heuristic.cc:30-118): one CTA per 32..128 x 128
 // output tile and no split-K on the hot call sites, i.e. 32-96 CTAs for N = 4096..12288.
 //
-// B200 design: stream-K over tcgen05.  A work unit is one 64-wide k-block of one 128-channel strip; the
-// units are cut into as many equal, contiguous ranges as CTAs fit on the GPU (two per SM), so all SMs
-// stream weights whatever N is, and a range that crosses a strip boundary simply ends one accumulation
-// and starts the next.  Per CTA:
-//   warp 0      weight producer: the two 4 KiB int8 tiles of a unit (1-D bulk copies), ring 7-8 deep;
-//   warp 10     activation producer: the BN x 64 tile of the unit (2-D tensor map, 128-byte swizzle, rows
-//               past M read as zeros), ring 6-8 deep (L2 hits, but as slow as DRAM while the weights stream);
-//   warps 2-5   int8 -> fp16 (exact), one thread per channel: its 64 bytes of the unit become 32 packed
+// B200 design: stream-K over tcgen05.  A work unit is two consecutive 64-wide k-blocks (one at the odd end
+// of K) of one 128-channel strip; the units are cut into as many equal, contiguous ranges as CTAs fit on
+// the GPU (two per SM), so all SMs stream weights whatever N is, and a range that crosses a strip boundary
+// simply ends one accumulation and starts the next.  Per CTA:
+//   warp 0      weight producer: the int8 tiles of a unit (two 1-D bulk copies of up to 8 KiB), ring 3-4 deep;
+//   warp 10     activation producer: the BN x 64 tiles of the unit's k-blocks (2-D tensor map, 128-byte
+//               swizzle, rows past M read as zeros), ring 3-4 deep - L2 hits, but as slow as DRAM while the
+//               weights stream;
+//   warps 2-5   int8 -> fp16 (exact), one thread per channel: its 64 bytes of a k-block become 32 packed
 //               half2 registers that go straight into TENSOR MEMORY (tcgen05.st, lane = channel), where the
 //               MMA reads its A operand from - the fp16 weights never exist in shared memory, which carries
-//               only the int8 bytes and the activations (a shared-memory fp16 copy made the kernel
-//               shared-memory-bandwidth-bound at about half the HBM rate);
-//   warp 1      tcgen05.mma M128 x BN x K16 with A from tensor memory, four per unit, fp32 accumulators in
+//               only the int8 bytes and the activations;
+//   warp 1      tcgen05.mma M128 x BN x K16 with A from tensor memory, eight per unit, fp32 accumulators in
 //               tensor memory too; two accumulator buffers alternate between consecutive strips;
 //   warps 6-9   epilogue: tcgen05.ld (lane = channel), then red.global.add.f32 into sums - 32 lanes of a
 //               warp hit 32 consecutive floats of one token row.
+// The producer and issuer roles are single threads, i.e. chains of dependent instructions; what they do per
+// unit (waits, address arithmetic, commits) bounds the kernel before any memory system does.  Hence units of
+// two k-blocks, ring positions kept as counters, and waits that cost one try_wait when the phase is complete.
 // Token tiles beyond the first (M > BN) are blockIdx.y: CTAs with the same blockIdx.x walk the same
 // weights at the same time and share them through L2.
 // Every wait is bounded (device status 2 on expiry) and the CTA frees its tensor memory on every path.
@@ -33,25 +36,35 @@ namespace eet {
 namespace {
 
 constexpr int kMidThreads = 352;
-// Ring depths.  Under the load of the weight stream every request - also an activation tile that hits L2 -
-// takes 4000-5000 cycles, and a CTA wants a unit every ~700 cycles: both rings must be 7-8 deep.
-constexpr int kMidNWMax = 8, kMidNXMax = 8;
-constexpr int kMidNH = 4;                            // fp16 weight buffers in TMEM
-constexpr int kMidACols = 32;                        // TMEM columns of one fp16 weight buffer: 64 k as half2
+constexpr int kMidUnitK = 2;                         // k-blocks per unit
+constexpr int kMidWStage = kMidUnitK * kTcW8Bytes;   // 16 KiB: [channel half][k-block][64 x 64 bytes]
+constexpr int kMidACols = kMidUnitK * 32;            // TMEM columns of one fp16 weight buffer: 64 k as half2 each
+constexpr int kMidNWMax = 4, kMidNXMax = 4, kMidNHMax = 4;
 
-__host__ __device__ constexpr int mid_nw(int bn) { return bn == 64 ? 7 : 8; }
-__host__ __device__ constexpr int mid_nx(int bn) { return bn == 32 ? 8 : 6; }
+__host__ __device__ constexpr int mid_nw(int bn) { return bn == 64 ? 3 : 4; }
+__host__ __device__ constexpr int mid_nx(int bn) { return bn == 32 ? 4 : 3; }
+__host__ __device__ constexpr int mid_nh(int bn) { return bn == 32 ? 3 : (bn == 64 ? 2 : 4); }
 
 __host__ __device__ constexpr int mid_smem_bytes(int bn)
 {
-    return mid_nw(bn) * kTcW8Bytes + mid_nx(bn) * bn * 128;
+    return mid_nw(bn) * kMidWStage + mid_nx(bn) * kMidUnitK * bn * 128;
 }
 
 // tensor-memory columns: two accumulators of BN columns, then the fp16 weight buffers
 __host__ __device__ constexpr uint32_t mid_tmem_cols(int bn)
 {
-    return 2 * bn + kMidNH * kMidACols <= 256 ? 256u : 512u;
+    return 2 * bn + mid_nh(bn) * kMidACols <= 256 ? 256u : 512u;
 }
+
+struct MidSmem {
+    uint64_t w_full[kMidNWMax], w_empty[kMidNWMax];     // int8 tiles landed / read by the 4 transform warps
+    uint64_t x_full[kMidNXMax], x_empty[kMidNXMax];     // activation tiles landed / their MMAs completed
+    uint64_t h_ready[kMidNHMax], h_empty[kMidNHMax];    // fp16 weights written (4 warps) / their MMAs completed
+    uint64_t acc_full[2];                               // all MMAs of a strip segment have completed
+    uint64_t acc_empty[2];                              // the epilogue warps have read the accumulator buffer (4 warps)
+    uint32_t tmem_base;
+    volatile int abort;
+};
 
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&v)[32])
 {
@@ -80,16 +93,6 @@ __device__ __forceinline__ void umma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, ui
         : "memory");
 }
 
-struct MidSmem {
-    uint64_t w_full[kMidNWMax], w_empty[kMidNWMax];     // int8 tiles landed / read by the 4 transform warps
-    uint64_t x_full[kMidNXMax], x_empty[kMidNXMax];     // activation tile landed / its MMAs completed
-    uint64_t h_ready[kMidNH], h_empty[kMidNH];    // fp16 weights written (4 warps) / their MMAs completed
-    uint64_t acc_full[2];                         // all MMAs of a strip segment have completed
-    uint64_t acc_empty[2];                        // the epilogue warps have read the accumulator buffer (4 warps)
-    uint32_t tmem_base;
-    volatile int abort;
-};
-
 __device__ __forceinline__ void red_add_f32(float* addr, float v)
 {
     asm volatile("red.global.add.f32 [%0], %1;" ::"l"(addr), "f"(v) : "memory");
@@ -102,15 +105,18 @@ gemm_mid_kernel(const __grid_constant__ CUtensorMap tmap_x, GemmArgs a)
     extern __shared__ __align__(1024) uint8_t mid_dyn[];
     __shared__ MidSmem sm;
     uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(mid_dyn) + 1023) & ~(uintptr_t)1023);
-    constexpr int kMidNW = mid_nw(BN), kMidNX = mid_nx(BN);
+    constexpr int kMidNW = mid_nw(BN), kMidNX = mid_nx(BN), kMidNH = mid_nh(BN);
+    constexpr int kXTile = BN * 128;                          // one k-block of activations
+    constexpr int kXStage = kMidUnitK * kXTile;
     uint8_t* x_ring = base;                                   // 1024-byte aligned tiles (swizzled)
-    uint8_t* w_ring = x_ring + kMidNX * BN * 128;
+    uint8_t* w_ring = x_ring + kMidNX * kXStage;
     constexpr uint32_t kTmemCols = mid_tmem_cols(BN);
     constexpr uint32_t kAColBase = 2 * BN;                    // first column of the fp16 weight buffers
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int KT = a.K / kTile;
-    const int strips1 = a.N / 128;                         // 128-channel strips of one matrix
-    const long long U = (long long)strips1 * KT * (a.B2 ? 2 : 1);
+    const int KP = (KT + kMidUnitK - 1) / kMidUnitK;          // units per strip
+    const int strips1 = a.N / 128;                            // 128-channel strips of one matrix
+    const long long U = (long long)strips1 * KP * (a.B2 ? 2 : 1);
     const int u0 = (int)(U * blockIdx.x / gridDim.x);
     const int u1 = (int)(U * (blockIdx.x + 1) / gridDim.x);
     const int m0 = blockIdx.y * BN;
@@ -152,27 +158,27 @@ gemm_mid_kernel(const __grid_constant__ CUtensorMap tmap_x, GemmArgs a)
         // ------------------------------------------------------------------ weight producer
         // (constant inputs: requested without waiting for the preceding kernel)
         if (lane == 0) {
-            // (ring slot, phase and the unit's coordinates advance as counters: this loop is one thread's
-            // dependent chain, an integer division per unit would show up in the kernel time)
             int s = 0, fill = 0;
             uint32_t ph = 1;   // parity of the previous round of slot s
-            int strip = u0 / KT, kb = u0 - strip * KT;
+            int strip = u0 / KP, kp = u0 - strip * KP;
             for (int u = u0; u < u1; ++u) {
                 if (fill >= kMidNW && !tc_wait(&sm.w_empty[s], ph, &sm.abort)) break;
+                const int kb = kp * kMidUnitK;
+                const uint32_t bytes = (uint32_t)min(kMidUnitK, KT - kb) * kTileBytes;   // per channel half
                 const uint8_t* Bm = (strip < strips1) ? a.B : a.B2;
                 const int st = (strip < strips1) ? strip : strip - strips1;
                 const uint8_t* w0 = Bm + ((size_t)(2 * st) * KT + kb) * kTileBytes;
-                uint8_t* dst = w_ring + (size_t)s * kTcW8Bytes;
-                mbar_arrive_expect_tx(&sm.w_full[s], (uint32_t)kTcW8Bytes);
-                bulk_g2s_stream(dst, w0, kTileBytes, &sm.w_full[s]);
-                bulk_g2s_stream(dst + kTileBytes, w0 + (size_t)KT * kTileBytes, kTileBytes, &sm.w_full[s]);
+                uint8_t* dst = w_ring + (size_t)s * kMidWStage;
+                mbar_arrive_expect_tx(&sm.w_full[s], 2 * bytes);
+                bulk_g2s_stream(dst, w0, bytes, &sm.w_full[s]);
+                bulk_g2s_stream(dst + kMidWStage / 2, w0 + (size_t)KT * kTileBytes, bytes, &sm.w_full[s]);
                 ++fill;
                 if (++s == kMidNW) {
                     s = 0;
                     ph ^= 1;
                 }
-                if (++kb == KT) {
-                    kb = 0;
+                if (++kp == KP) {
+                    kp = 0;
                     ++strip;
                 }
             }
@@ -184,17 +190,21 @@ gemm_mid_kernel(const __grid_constant__ CUtensorMap tmap_x, GemmArgs a)
             pdl_wait();   // the activations are the preceding kernel's output
             int s = 0, fill = 0;
             uint32_t ph = 1;
-            int kb = u0 % KT;
+            int kp = u0 % KP;
             for (int u = u0; u < u1; ++u) {
                 if (fill >= kMidNX && !tc_wait(&sm.x_empty[s], ph, &sm.abort)) break;
-                mbar_arrive_expect_tx(&sm.x_full[s], (uint32_t)(BN * 128));
-                tma_load_2d(x_ring + (size_t)s * BN * 128, &tmap_x, kb * kTile, m0, &sm.x_full[s]);
+                const int kb = kp * kMidUnitK;
+                const bool two = kb + 1 < KT;
+                uint8_t* dst = x_ring + (size_t)s * kXStage;
+                mbar_arrive_expect_tx(&sm.x_full[s], (uint32_t)(two ? 2 * kXTile : kXTile));
+                tma_load_2d(dst, &tmap_x, kb * kTile, m0, &sm.x_full[s]);
+                if (two) tma_load_2d(dst + kXTile, &tmap_x, (kb + 1) * kTile, m0, &sm.x_full[s]);
                 ++fill;
                 if (++s == kMidNX) {
                     s = 0;
                     ph ^= 1;
                 }
-                if (++kb == KT) kb = 0;
+                if (++kp == KP) kp = 0;
             }
         }
     }
@@ -207,7 +217,8 @@ gemm_mid_kernel(const __grid_constant__ CUtensorMap tmap_x, GemmArgs a)
             int sx = 0, sh = 0, seg = 0;
             uint32_t phx = 0, phh = 0;
             bool ok = true;
-            int strip_end = (u0 / KT + 1) * KT;   // first unit of the next strip
+            int strip_end = (u0 / KP + 1) * KP;   // first unit of the next strip
+            const bool odd_tail = (KT & 1) != 0;  // the last unit of a strip then holds one k-block
             for (int u = u0; u < u1 && ok;) {
                 const int u_end = min(u1, strip_end);
                 const int buf = seg & 1;
@@ -221,12 +232,19 @@ gemm_mid_kernel(const __grid_constant__ CUtensorMap tmap_x, GemmArgs a)
                     }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint32_t a_tmem = a_tmem0 + (uint32_t)(sh * kMidACols);
-                    const uint64_t b_desc = b_desc0 + (uint64_t)(sx * (BN * 128 >> 4));
+                    const uint64_t b_desc = b_desc0 + (uint64_t)(sx * (kXStage >> 4));
                     // 16 reduction indices per MMA: 8 columns of A, 32 bytes along the swizzled row of B
                     umma_f16_ts(d_tmem, a_tmem, b_desc, idesc, uu > u);
                     umma_f16_ts(d_tmem, a_tmem + 8, b_desc + 2, idesc, true);
                     umma_f16_ts(d_tmem, a_tmem + 16, b_desc + 4, idesc, true);
                     umma_f16_ts(d_tmem, a_tmem + 24, b_desc + 6, idesc, true);
+                    if (!(odd_tail && uu + 1 == strip_end)) {
+                        const uint64_t b2 = b_desc + (uint64_t)(kXTile >> 4);
+                        umma_f16_ts(d_tmem, a_tmem + 32, b2, idesc, true);
+                        umma_f16_ts(d_tmem, a_tmem + 40, b2 + 2, idesc, true);
+                        umma_f16_ts(d_tmem, a_tmem + 48, b2 + 4, idesc, true);
+                        umma_f16_ts(d_tmem, a_tmem + 56, b2 + 6, idesc, true);
+                    }
                     umma_commit(&sm.h_empty[sh]);
                     umma_commit(&sm.x_empty[sx]);
                     if (++sx == kMidNX) {
@@ -240,7 +258,7 @@ gemm_mid_kernel(const __grid_constant__ CUtensorMap tmap_x, GemmArgs a)
                 }
                 if (ok) umma_commit(&sm.acc_full[buf]);
                 u = u_end;
-                strip_end += KT;
+                strip_end += KP;
                 ++seg;
             }
         }
@@ -249,38 +267,58 @@ gemm_mid_kernel(const __grid_constant__ CUtensorMap tmap_x, GemmArgs a)
         // ------------------------------------------------------------------ transform warps
         // this thread's channel: TMEM lane = 32 * (warp % 4) + lane (the lanes a warp may access)
         const int r = (warp & 3) * 32 + lane;
-        const int sx = (lane >> 1) & 3;   // 16-byte chunks are read in XOR order: conflict-free for 64-byte rows
+        const int sxr = (lane >> 1) & 3;   // 16-byte chunks are read in XOR order: conflict-free for 64-byte rows
+        const uint32_t row_off = (uint32_t)((r >> 6) * (kMidWStage / 2) + (r & 63) * 64);
+        const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
         int sw = 0, sh = 0, fill = 0;
         uint32_t phw = 0, phh = 1;
+        int kp = u0 % KP;
         for (int u = u0; u < u1; ++u) {
             if (!tc_wait(&sm.w_full[sw], phw, &sm.abort)) break;
-            const uint8_t* row = w_ring + (size_t)sw * kTcW8Bytes + r * 64;
-            uint4 c[4];
+            const int nk = (kp * kMidUnitK + 1 < KT) ? 2 : 1;
+            const uint8_t* row = w_ring + (size_t)sw * kMidWStage + row_off;
+            uint4 c[kMidUnitK][4];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) c[j] = *reinterpret_cast<const uint4*>(row + ((j ^ sx) << 4));
+            for (int kk = 0; kk < kMidUnitK; ++kk) {
+                if (kk < nk) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        c[kk][j] = *reinterpret_cast<const uint4*>(row + kk * kTileBytes + ((j ^ sxr) << 4));
+                    }
+                }
+            }
             // the int8 stage is free again as soon as the bytes are in registers
             __syncwarp();
             if (lane == 0) mbar_arrive(&sm.w_empty[sw]);
-            // c[j] holds chunk j ^ sx: undo the permutation with two conditional swap stages
-            if (sx & 1) {
-                uint4 t = c[0]; c[0] = c[1]; c[1] = t;
-                t = c[2]; c[2] = c[3]; c[3] = t;
-            }
-            if (sx & 2) {
-                uint4 t = c[0]; c[0] = c[2]; c[2] = t;
-                t = c[1]; c[1] = c[3]; c[3] = t;
-            }
-            uint32_t h[32];
+            bool live = true;
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                cvt_u8x4_to_f16x4(c[j].x, h[8 * j + 0], h[8 * j + 1]);
-                cvt_u8x4_to_f16x4(c[j].y, h[8 * j + 2], h[8 * j + 3]);
-                cvt_u8x4_to_f16x4(c[j].z, h[8 * j + 4], h[8 * j + 5]);
-                cvt_u8x4_to_f16x4(c[j].w, h[8 * j + 6], h[8 * j + 7]);
+            for (int kk = 0; kk < kMidUnitK; ++kk) {
+                if (kk < nk && live) {
+                    // c[kk][j] holds chunk j ^ sxr: undo the permutation with two conditional swap stages
+                    if (sxr & 1) {
+                        uint4 t = c[kk][0]; c[kk][0] = c[kk][1]; c[kk][1] = t;
+                        t = c[kk][2]; c[kk][2] = c[kk][3]; c[kk][3] = t;
+                    }
+                    if (sxr & 2) {
+                        uint4 t = c[kk][0]; c[kk][0] = c[kk][2]; c[kk][2] = t;
+                        t = c[kk][1]; c[kk][1] = c[kk][3]; c[kk][3] = t;
+                    }
+                    uint32_t h[32];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        cvt_u8x4_to_f16x4(c[kk][j].x, h[8 * j + 0], h[8 * j + 1]);
+                        cvt_u8x4_to_f16x4(c[kk][j].y, h[8 * j + 2], h[8 * j + 3]);
+                        cvt_u8x4_to_f16x4(c[kk][j].z, h[8 * j + 4], h[8 * j + 5]);
+                        cvt_u8x4_to_f16x4(c[kk][j].w, h[8 * j + 6], h[8 * j + 7]);
+                    }
+                    if (kk == 0) {
+                        if (fill >= kMidNH && !tc_wait(&sm.h_empty[sh], phh, &sm.abort)) live = false;
+                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    }
+                    if (live) tmem_st32(tmem + lane_addr + kAColBase + (uint32_t)(sh * kMidACols + kk * 32), h);
+                }
             }
-            if (fill >= kMidNH && !tc_wait(&sm.h_empty[sh], phh, &sm.abort)) break;
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            tmem_st32(tmem + ((uint32_t)((warp & 3) * 32) << 16) + kAColBase + (uint32_t)(sh * kMidACols), h);
+            if (!live) break;
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(&sm.h_ready[sh]);
@@ -293,6 +331,7 @@ gemm_mid_kernel(const __grid_constant__ CUtensorMap tmap_x, GemmArgs a)
                 sh = 0;
                 phh ^= 1;
             }
+            if (++kp == KP) kp = 0;
         }
     }
     else if (warp >= 10) {
@@ -304,8 +343,8 @@ gemm_mid_kernel(const __grid_constant__ CUtensorMap tmap_x, GemmArgs a)
         const int lane_base = (warp & 3) * 32;   // the TMEM lanes this warp may read
         int seg = 0;
         for (int u = u0; u < u1; ++seg) {
-            const int strip = u / KT;
-            const int u_end = min(u1, (strip + 1) * KT);
+            const int strip = u / KP;
+            const int u_end = min(u1, (strip + 1) * KP);
             const int buf = seg & 1;
             // one lane polls (a segment lasts tens of microseconds: 128 spinning lanes would take issue
             // slots and shared-memory bandwidth from the threads that feed the tensor core)
@@ -356,7 +395,7 @@ int launch_mid(const CUtensorMap& map, const GemmArgs& a, cudaStream_t stream)
         attr_set[dev] = true;
     }
     const int m_tiles = (a.M + BN - 1) / BN;
-    const long long U = (long long)(a.N / 128) * (a.K / kTile) * (a.B2 ? 2 : 1);
+    const long long U = (long long)(a.N / 128) * ((a.K / kTile + kMidUnitK - 1) / kMidUnitK) * (a.B2 ? 2 : 1);
     int grid_x = (BN <= 64 ? 2 : 1) * sm_count() / m_tiles;
     if (grid_x < 1) grid_x = 1;
     if (grid_x > U) grid_x = (int)U;

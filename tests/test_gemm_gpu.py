@@ -174,7 +174,7 @@ def test_baichuan13b_and_llama65b_projection_shapes(KN):
 
 
 @pytest.mark.parametrize("M", [17, 32, 40, 64, 100, 128, 250, 256])
-@pytest.mark.parametrize("KN", [(256, 128), (1024, 384), (4096, 4096)])
+@pytest.mark.parametrize("KN", [(256, 128), (192, 256), (1024, 384), (4096, 4096)])
 def test_stream_k_tensor_core_kernel(KN, M):
     """16 < M <= 256 goes to the stream-K tcgen05 kernel: token tiles of 32 / 64 / 128 with ragged tails,
     strips that end inside a CTA's range (small K) and ranges shorter than a strip (large K)."""
