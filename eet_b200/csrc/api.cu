@@ -136,7 +136,7 @@ static int mid_use_max_m()
     static int v = -1;
     if (v < 0) {
         const char* e = getenv("EET_MID_MAX_M");
-        v = e ? atoi(e) : 256;
+        v = e ? atoi(e) : 512;
         if (v > kMidMaxM) v = kMidMaxM;
     }
     return v;

@@ -373,26 +373,37 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t* __res
     if (warp == 0) {
         // ------------------------------------------------------------------ activation producer
         if (lane == 0) {
+            // (ring positions are counters: this loop is one thread's chain of dependent instructions)
+            int s = 0;
+            uint32_t ph = 1;
             for (int kb = 0; kb < KT; ++kb) {
-                const int s = kb % kTc2NX;
-                if (kb >= kTc2NX && !tc_wait(&sm.x_empty[s], ((kb / kTc2NX) - 1) & 1, &sm.abort)) break;
+                if (kb >= kTc2NX && !tc_wait(&sm.x_empty[s], ph, &sm.abort)) break;
                 mbar_arrive_expect_tx(&sm.x_full[s], (uint32_t)kTc2XBytes);
                 tma_load_2d(x_ring + (size_t)s * kTc2XBytes, &tmap_x, kb * kTile, m0, &sm.x_full[s]);
+                if (++s == kTc2NX) {
+                    s = 0;
+                    ph ^= 1;
+                }
             }
         }
     }
     else if (warp == 6) {
         // ------------------------------------------------------------------ int8 weight producer
         if (lane == 0) {
-            for (int kb = 0; kb < KT; ++kb) {
-                const int s = kb % kTc2NW;
-                if (kb >= kTc2NW && !tc_wait(&sm.w_empty[s], ((kb / kTc2NW) - 1) & 1, &sm.abort)) break;
+            int s = 0;
+            uint32_t ph = 1;
+            const uint8_t* w0 = Bw + (size_t)(n0 / kTile) * KT * kTileBytes;
+            for (int kb = 0; kb < KT; ++kb, w0 += kTileBytes) {
+                if (kb >= kTc2NW && !tc_wait(&sm.w_empty[s], ph, &sm.abort)) break;
                 mbar_arrive_expect_tx(&sm.w_full[s], (uint32_t)kTc2WBytes);
-                const uint8_t* w0 = Bw + ((size_t)(n0 / kTile) * KT + kb) * kTileBytes;
                 uint8_t* dst = w_ring + (size_t)s * kTc2WBytes;
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                     bulk_g2s(dst + i * kTileBytes, w0 + (size_t)i * KT * kTileBytes, kTileBytes, &sm.w_full[s]);
+                }
+                if (++s == kTc2NW) {
+                    s = 0;
+                    ph ^= 1;
                 }
             }
         }
@@ -401,28 +412,38 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t* __res
         // ------------------------------------------------------------------ MMA issuer
         if (lane == 0) {
             constexpr uint32_t idesc = umma_idesc_f16(128, 256);
+            const uint64_t b_desc0 = umma_desc_sw128(smem_u32(x_ring));
+            const uint64_t a_desc0 = umma_desc_sw128(smem_u32(h_ring));
+            int sx = 0, su = 0;
+            uint32_t phx = 0, phu = 0;
             bool ok = true;
             for (int kb = 0; kb < KT && ok; ++kb) {
-                const int sx = kb % kTc2NX;
-                if (!tc_wait(&sm.x_full[sx], (kb / kTc2NX) & 1, &sm.abort)) break;
-                const uint64_t b_desc = umma_desc_sw128(smem_u32(x_ring + (size_t)sx * kTc2XBytes));
+                if (!tc_wait(&sm.x_full[sx], phx, &sm.abort)) break;
+                const uint64_t b_desc = b_desc0 + (uint64_t)(sx * (kTc2XBytes >> 4));
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
-                    const int u = 2 * kb + h, su = u % kTc2NH;
-                    if (!tc_wait(&sm.h_ready[su], (u / kTc2NH) & 1, &sm.abort)) {
+                    if (!tc_wait(&sm.h_ready[su], phu, &sm.abort)) {
                         ok = false;
                         break;
                     }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const uint64_t a_desc = umma_desc_sw128(smem_u32(h_ring + (size_t)su * kTc2HBytes));
-#pragma unroll
-                    for (int k = 0; k < 4; ++k) {
-                        umma_f16(tmem + (uint32_t)(h * 256), a_desc + (uint64_t)(2 * k), b_desc + (uint64_t)(2 * k), idesc,
-                                 (kb | k) != 0);
-                    }
+                    const uint64_t a_desc = a_desc0 + (uint64_t)(su * (kTc2HBytes >> 4));
+                    const uint32_t d = tmem + (uint32_t)(h * 256);
+                    umma_f16(d, a_desc, b_desc, idesc, kb != 0);
+                    umma_f16(d, a_desc + 2, b_desc + 2, idesc, true);
+                    umma_f16(d, a_desc + 4, b_desc + 4, idesc, true);
+                    umma_f16(d, a_desc + 6, b_desc + 6, idesc, true);
                     umma_commit(&sm.h_empty[su]);
+                    if (++su == kTc2NH) {
+                        su = 0;
+                        phu ^= 1;
+                    }
                 }
                 if (ok) umma_commit(&sm.x_empty[sx]);
+                if (++sx == kTc2NX) {
+                    sx = 0;
+                    phx ^= 1;
+                }
             }
             umma_commit(&sm.accum);
         }
@@ -431,14 +452,14 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t* __res
         // ------------------------------------------------------------------ transform warps, then epilogue
         const int tw = threadIdx.x - 64;  // 0..127
         bool ok = true;
+        int sw = 0, su = 0, filled = 0;
+        uint32_t phw = 0, phu = 1;
         for (int kb = 0; kb < KT && ok; ++kb) {
-            const int sw = kb % kTc2NW;
-            if (!tc_wait(&sm.w_full[sw], (kb / kTc2NW) & 1, &sm.abort)) break;
+            if (!tc_wait(&sm.w_full[sw], phw, &sm.abort)) break;
             const uint8_t* w8 = w_ring + (size_t)sw * kTc2WBytes;
 #pragma unroll 1
             for (int h = 0; h < 2; ++h) {
-                const int u = 2 * kb + h, su = u % kTc2NH;
-                if (u >= kTc2NH && !tc_wait(&sm.h_empty[su], ((u / kTc2NH) - 1) & 1, &sm.abort)) {
+                if (filled >= kTc2NH && !tc_wait(&sm.h_empty[su], phu, &sm.abort)) {
                     ok = false;
                     break;
                 }
@@ -460,10 +481,19 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t* __res
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&sm.h_ready[su]);
+                ++filled;
+                if (++su == kTc2NH) {
+                    su = 0;
+                    phu ^= 1;
+                }
             }
             if (ok) {
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&sm.w_empty[sw]);
+            }
+            if (++sw == kTc2NW) {
+                sw = 0;
+                phw ^= 1;
             }
         }
 

@@ -173,10 +173,10 @@ def test_baichuan13b_and_llama65b_projection_shapes(KN):
     assert ((y[rows].double() - ref).abs() <= 1e-2 * ref.abs().amax(1, keepdim=True)).all()
 
 
-@pytest.mark.parametrize("M", [17, 32, 40, 64, 100, 128, 250, 256])
+@pytest.mark.parametrize("M", [17, 32, 40, 64, 100, 128, 250, 256, 400, 512])
 @pytest.mark.parametrize("KN", [(256, 128), (192, 256), (1024, 384), (4096, 4096)])
 def test_stream_k_tensor_core_kernel(KN, M):
-    """16 < M <= 256 goes to the stream-K tcgen05 kernel: token tiles of 32 / 64 / 128 with ragged tails,
+    """16 < M <= 512 goes to the stream-K tcgen05 kernel: token tiles of 32 / 64 / 128 with ragged tails,
     strips that end inside a CTA's range (small K) and ranges shorter than a strip (large K)."""
     x, q, s = _case(KN[0], KN[1], M, seed=M + KN[1])
     _check(_run(x, q, s), x, q, s)
