@@ -301,10 +301,9 @@ def _norm_head(x2d, gamma, eps, xn):
     p = _pending.pop(x2d.data_ptr(), None)
     if p is not None and p.peer is not None:
         pb, which = p.peer
-        check(lib.eet_rmsnorm_finalize_tp(pb.sum_ptrs[which], pb.flag_ptrs, pb.tp.size, pb.tp.rank, pb.epochs.data_ptr(),
-                                          pb.buffer(1 - which, pb.ROWS).data_ptr(), p.scale.data_ptr(),
-                                          p.residual.data_ptr(), x2d.data_ptr(), gamma.data_ptr(), xn.data_ptr(), M, n,
-                                          eps, _stream()))
+        check(lib.eet_rmsnorm_finalize_tp(p.sums.data_ptr(), pb.inbox_ptrs, pb.tp.size, pb.tp.rank, which,
+                                          pb.epochs.data_ptr(), p.scale.data_ptr(), p.residual.data_ptr(),
+                                          x2d.data_ptr(), gamma.data_ptr(), xn.data_ptr(), M, n, eps, _stream()))
     elif p is not None:
         check(lib.eet_rmsnorm_finalize(p.sums.data_ptr(), p.scale.data_ptr(), p.residual.data_ptr(), x2d.data_ptr(),
                                        gamma.data_ptr(), xn.data_ptr(), M, n, eps, _stream()))

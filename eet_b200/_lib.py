@@ -28,7 +28,7 @@ SIGNATURES = {
     "eet_gemm_w8a16_accum": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp, _vp, _vp]),
     "eet_gemm_w8a16_finalize": (_i, [_vp, _vp, _vp, _vp, _i, _i, _vp]),
     "eet_rmsnorm_finalize": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _f, _vp]),
-    "eet_rmsnorm_finalize_tp": (_i, [_vp, _vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _f, _vp]),
+    "eet_rmsnorm_finalize_tp": (_i, [_vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _f, _vp]),
     "eet_swiglu_finalize": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _vp]),
     "eet_rmsnorm": (_i, [_vp, _vp, _vp, _i, _i, _f, _vp]),
     "eet_swiglu": (_i, [_vp, _vp, _i, _i, _vp]),

@@ -276,16 +276,16 @@ int eet_rmsnorm_finalize(float* sums, const void* scale, const void* residual, v
                                    (const __half*)gamma, (__half*)xn_out, M, n, eps, (cudaStream_t)stream);
 }
 
-int eet_rmsnorm_finalize_tp(const float* const* peer_sums, int* const* peer_flags, int world, int rank, int* epochs,
-                            float* zero_local, const void* scale, const void* residual, void* h_out, const void* gamma,
-                            void* xn_out, int M, int n, float eps, void* stream)
+int eet_rmsnorm_finalize_tp(float* local_sums, void* const* peer_inbox, int world, int rank, int which, int* epochs,
+                            const void* scale, const void* residual, void* h_out, const void* gamma, void* xn_out, int M,
+                            int n, float eps, void* stream)
 {
-    EET_CHECK(peer_sums && peer_flags && epochs && zero_local && scale && residual && h_out && gamma && xn_out,
+    EET_CHECK(local_sums && peer_inbox && epochs && scale && residual && h_out && gamma && xn_out,
               "eet_rmsnorm_finalize_tp: NULL argument");
-    EET_CHECK(aligned16(zero_local) && aligned16(scale) && aligned16(residual) && aligned16(h_out) && aligned16(gamma) &&
+    EET_CHECK(aligned16(local_sums) && aligned16(scale) && aligned16(residual) && aligned16(h_out) && aligned16(gamma) &&
                   aligned16(xn_out),
               "eet_rmsnorm_finalize_tp: pointers must be 16-byte aligned");
-    return launch_rmsnorm_finalize_tp(peer_sums, peer_flags, world, rank, epochs, zero_local, (const __half*)scale,
+    return launch_rmsnorm_finalize_tp(local_sums, peer_inbox, world, rank, which, epochs, (const __half*)scale,
                                       (const __half*)residual, (__half*)h_out, (const __half*)gamma, (__half*)xn_out, M,
                                       n, eps, (cudaStream_t)stream);
 }

@@ -194,24 +194,31 @@ rmsnorm_finalize_kernel(float* __restrict__ sums, const __half* __restrict__ sca
 }
 
 // Tensor-parallel form of rmsnorm_finalize_kernel: the all-reduce of a row-parallel projection fused into
-// the kernel that consumes it.  Every rank's GEMM has left its partial sums in a buffer that the other
-// ranks can read (peer memory over NVLink); a row's CTA first meets the same row's CTAs of the other ranks
-// at a flag barrier (each writes its epoch into every peer's flag array, then waits - for a bounded
-// number of polls - until all peers' epochs have arrived), then adds the `world` partial rows in fp32 in
-// rank order (so every rank computes bit-identical sums), applies scale and residual and normalises as the
-// single-GPU kernel does.  Two sum buffers alternate (attention output projection / FFN down projection):
-// this kernel zeroes the local copy of the one it does NOT read, which every rank finished reading before
-// it could pass this call's barrier.
+// the kernel that consumes it, with the latency of ONE NVLink hop.  Every rank's GEMM has left its partial
+// sums in local memory.  A row's CTA pushes them into an inbox in every peer's memory (peer stores over
+// NVLink) as 8-byte pairs {value bits, epoch}: a pair is written atomically, so the receiver needs no
+// separate flag and no fence - it polls its own (local) inbox until the pairs carry the epoch of this
+// exchange, the scheme of NCCL's low-latency protocol.  The partial rows are added in fp32 in rank order, so
+// every rank forms bit-identical sums; then scale, residual and RMSNorm as on one GPU.  Two inboxes
+// alternate (attention output projection / FFN down projection): a peer can overwrite an inbox only after
+// the exchange in between, which needs this rank's push, which follows this rank's reads.
 struct TpPeers {
-    const float* sums[8];   // the buffer to reduce, on every rank (index = rank)
-    int* flags[8];          // every rank's flag array [16 rows][8 ranks]
-    int world, rank;
+    uint2* inbox[8];   // every rank's inbox [2][8 source ranks][16 rows][n] of {float bits, epoch} (index = rank)
+    int world, rank, which;
 };
 
 constexpr uint32_t kTpSpinLimit = 1u << 22;
+constexpr int kTpRows = 16;
+
+__device__ __forceinline__ uint4 ld_volatile_u4(const void* p)
+{
+    uint4 v;
+    asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
 
 __global__ void __launch_bounds__(1024)
-rmsnorm_finalize_tp_kernel(TpPeers peers, int* __restrict__ epochs, float* __restrict__ zero_local,
+rmsnorm_finalize_tp_kernel(TpPeers peers, float* __restrict__ local_sums, int* __restrict__ epochs,
                            const __half* __restrict__ scale, const __half* __restrict__ residual,
                            __half* __restrict__ h_out, const __half* __restrict__ gamma, __half* __restrict__ xn_out,
                            int n, float eps)
@@ -223,30 +230,40 @@ rmsnorm_finalize_tp_kernel(TpPeers peers, int* __restrict__ epochs, float* __res
     pdl_wait();   // this rank's GEMM (and everything before it) is complete
     const int row = blockIdx.x;
     if (threadIdx.x == 0) {
-        s_epoch = epochs[row] + 1;
-        epochs[row] = s_epoch;
-        __threadfence_system();
+        s_epoch = epochs[peers.which * kTpRows + row] + 1;
+        epochs[peers.which * kTpRows + row] = s_epoch;
     }
     __syncthreads();
-    const int epoch = s_epoch;
-    if (threadIdx.x < peers.world) {
-        // announce: my partial sums of this row are final
-        volatile int* theirs = peers.flags[threadIdx.x] + row * 8 + peers.rank;
-        *theirs = epoch;
-        // wait for the same announcement from rank threadIdx.x
-        volatile int* mine = peers.flags[peers.rank] + row * 8 + threadIdx.x;
-        uint32_t spins = 0;
-        while (*mine < epoch) {
-            if (++spins > kTpSpinLimit) {
-                g_device_status = 4;   // a peer never arrived: give up, the host reads the status word
-                break;
+    const uint32_t epoch = (uint32_t)s_epoch;
+    const int nv = n >> 3;
+    const size_t slot_row = (size_t)(peers.which * 8) * kTpRows * n + (size_t)row * n;   // + src * kTpRows * n
+
+    // ---- push this rank's partial row to every peer, keep a copy, zero the local sums for the next GEMM ----
+    float mine[2][8];
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+        const int i = threadIdx.x + j * blockDim.x;
+        if (i < nv) {
+            float4* lp = reinterpret_cast<float4*>(local_sums + (size_t)row * n + (size_t)i * 8);
+            const float4 a = lp[0], b = lp[1];
+            mine[j][0] = a.x; mine[j][1] = a.y; mine[j][2] = a.z; mine[j][3] = a.w;
+            mine[j][4] = b.x; mine[j][5] = b.y; mine[j][6] = b.z; mine[j][7] = b.w;
+            const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+            lp[0] = z;
+            lp[1] = z;
+            for (int p = 0; p < peers.world; ++p) {
+                if (p == peers.rank) continue;
+                uint4* dst = reinterpret_cast<uint4*>(peers.inbox[p] + slot_row + (size_t)peers.rank * kTpRows * n +
+                                                      (size_t)i * 8);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    dst[e] = make_uint4(__float_as_uint(mine[j][2 * e]), epoch, __float_as_uint(mine[j][2 * e + 1]), epoch);
+                }
             }
         }
-        __threadfence_system();
     }
-    __syncthreads();
 
-    const int nv = n >> 3;
+    // ---- collect: poll the local inbox until every peer's pairs carry this epoch, add in rank order ----
     const uint4* rr = reinterpret_cast<const uint4*>(residual + (size_t)row * n);
     uint4 h[2];
     float ss = 0.f;
@@ -254,31 +271,37 @@ rmsnorm_finalize_tp_kernel(TpPeers peers, int* __restrict__ epochs, float* __res
     for (int j = 0; j < 2; ++j) {
         const int i = threadIdx.x + j * blockDim.x;
         if (i < nv) {
-            // all ranks' 32 bytes are requested before any is used, so the NVLink round trips overlap;
-            // .cv loads: peer memory is read at its home, never from a stale local cache line
-            float4 pa[8], pb[8];
-#pragma unroll
-            for (int r = 0; r < 8; ++r) {
-                if (r < peers.world) {
-                    const float4* p = reinterpret_cast<const float4*>(peers.sums[r] + (size_t)row * n + (size_t)i * 8);
-                    pa[r] = __ldcv(p);
-                    pb[r] = __ldcv(p + 1);
-                }
-            }
             float v[8];
 #pragma unroll
             for (int e = 0; e < 8; ++e) v[e] = 0.f;
+            for (int r = 0; r < peers.world; ++r) {
+                if (r == peers.rank) {
 #pragma unroll
-            for (int r = 0; r < 8; ++r) {   // fixed rank order: every rank forms bit-identical sums
-                if (r < peers.world) {
-                    v[0] += pa[r].x; v[1] += pa[r].y; v[2] += pa[r].z; v[3] += pa[r].w;
-                    v[4] += pb[r].x; v[5] += pb[r].y; v[6] += pb[r].z; v[7] += pb[r].w;
+                    for (int e = 0; e < 8; ++e) v[e] += mine[j][e];
+                    continue;
+                }
+                const uint4* src = reinterpret_cast<const uint4*>(peers.inbox[peers.rank] + slot_row +
+                                                                  (size_t)r * kTpRows * n + (size_t)i * 8);
+                uint4 c[4];
+                uint32_t spins = 0;
+                while (true) {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) c[e] = ld_volatile_u4(src + e);
+                    bool ok = true;
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) ok = ok && c[e].y == epoch && c[e].w == epoch;
+                    if (ok) break;
+                    if (++spins > kTpSpinLimit) {
+                        g_device_status = 4;   // a peer never arrived: give up, the host reads the status word
+                        break;
+                    }
+                }
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    v[2 * e] += __uint_as_float(c[e].x);
+                    v[2 * e + 1] += __uint_as_float(c[e].z);
                 }
             }
-            const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
-            float4* zp = reinterpret_cast<float4*>(zero_local + (size_t)row * n + (size_t)i * 8);
-            zp[0] = z;
-            zp[1] = z;
             h[j] = rr[i];
             const uint4 sc = reinterpret_cast<const uint4*>(scale)[i];
             h[j] = finalize8(v, sc, &h[j]);
@@ -512,28 +535,29 @@ int launch_rmsnorm_finalize(float* sums, const __half* scale, const __half* resi
     return 0;
 }
 
-int launch_rmsnorm_finalize_tp(const float* const* peer_sums, int* const* peer_flags, int world, int rank, int* epochs,
-                               float* zero_local, const __half* scale, const __half* residual, __half* h_out,
-                               const __half* gamma, __half* xn_out, int M, int n, float eps, cudaStream_t stream)
+int launch_rmsnorm_finalize_tp(float* local_sums, void* const* peer_inbox, int world, int rank, int which, int* epochs,
+                               const __half* scale, const __half* residual, __half* h_out, const __half* gamma,
+                               __half* xn_out, int M, int n, float eps, cudaStream_t stream)
 {
     EET_CHECK(n % 8 == 0 && n > 0 && n <= 16384, "rmsnorm: hidden size %d must be a multiple of 8 and <= 16384", n);
     EET_CHECK(world >= 1 && world <= 8 && rank >= 0 && rank < world, "tensor-parallel rmsnorm: bad world %d / rank %d",
               world, rank);
-    EET_CHECK(M <= 16, "tensor-parallel rmsnorm: at most 16 rows (decode regime), got %d", M);
+    EET_CHECK(which == 0 || which == 1, "tensor-parallel rmsnorm: inbox index %d must be 0 or 1", which);
+    EET_CHECK(M <= kTpRows, "tensor-parallel rmsnorm: at most 16 rows (decode regime), got %d", M);
     if (M == 0) return 0;
     TpPeers peers = {};
     for (int r = 0; r < world; ++r) {
-        EET_CHECK(peer_sums[r] != nullptr && peer_flags[r] != nullptr, "tensor-parallel rmsnorm: NULL peer pointer");
-        peers.sums[r] = peer_sums[r];
-        peers.flags[r] = peer_flags[r];
+        EET_CHECK(peer_inbox[r] != nullptr, "tensor-parallel rmsnorm: NULL peer pointer");
+        peers.inbox[r] = reinterpret_cast<uint2*>(peer_inbox[r]);
     }
     peers.world = world;
     peers.rank = rank;
+    peers.which = which;
     const int nv = n / 8;
     int threads = ((nv + 1) / 2 + 31) / 32 * 32;
     if (threads < 32) threads = 32;
     if (threads > 1024) threads = 1024;
-    EET_CUDA(launch_pdl(rmsnorm_finalize_tp_kernel, dim3(M), dim3(threads), 0, stream, peers, epochs, zero_local, scale,
+    EET_CUDA(launch_pdl(rmsnorm_finalize_tp_kernel, dim3(M), dim3(threads), 0, stream, peers, local_sums, epochs, scale,
                         residual, h_out, gamma, xn_out, n, eps));
     return 0;
 }

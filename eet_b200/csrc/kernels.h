@@ -48,9 +48,9 @@ int launch_finalize(float* sums, const __half* scale, const __half* residual, __
                     cudaStream_t stream);
 int launch_rmsnorm_finalize(float* sums, const __half* scale, const __half* residual, __half* h_out,
                             const __half* gamma, __half* xn_out, int M, int n, float eps, cudaStream_t stream);
-int launch_rmsnorm_finalize_tp(const float* const* peer_sums, int* const* peer_flags, int world, int rank, int* epochs,
-                               float* zero_local, const __half* scale, const __half* residual, __half* h_out,
-                               const __half* gamma, __half* xn_out, int M, int n, float eps, cudaStream_t stream);
+int launch_rmsnorm_finalize_tp(float* local_sums, void* const* peer_inbox, int world, int rank, int which, int* epochs,
+                               const __half* scale, const __half* residual, __half* h_out, const __half* gamma,
+                               __half* xn_out, int M, int n, float eps, cudaStream_t stream);
 int launch_swiglu_finalize(float* gate_sums, const __half* gate_scale, float* up_sums, const __half* up_scale,
                            __half* act_out, int M, int n, cudaStream_t stream);
 int launch_swiglu(__half* gate_inout, const __half* up, int M, int n, cudaStream_t stream);

@@ -37,11 +37,11 @@ class TensorParallel:
 
 
 class PeerBuffers:
-    """Memory of every rank that all ranks can address from their kernels: two fp32 partial-sum buffers
-    [rows][hidden] (attention-output / FFN-down projections alternate between them) and a flag array, shared
-    through CUDA IPC handles exchanged over the process group.  Lets the decode path replace
-    `NCCL all-reduce -> RMSNorm` by one kernel that reads the peers' partial sums over NVLink
-    (eet_rmsnorm_finalize_tp)."""
+    """What the fused tensor-parallel reduction needs on every rank: two local fp32 partial-sum buffers
+    [rows][hidden] (attention-output / FFN-down projections alternate between them), and an inbox
+    [2][8 source ranks][rows][hidden] of {float bits, epoch} pairs that the OTHER ranks write into over NVLink.
+    The inboxes are shared through CUDA IPC handles exchanged over the process group.  Lets the decode path
+    replace `NCCL all-reduce -> RMSNorm` by one kernel (eet_rmsnorm_finalize_tp)."""
 
     ROWS = 16
 
@@ -54,13 +54,12 @@ class PeerBuffers:
         self.tp, self.hidden = tp, hidden
         n = self.ROWS * hidden
         self.local_sums = torch.zeros(2 * n, dtype=torch.float32, device=device)
-        self.local_flags = torch.zeros(self.ROWS * 8, dtype=torch.int32, device=device)
-        self.epochs = torch.zeros(self.ROWS, dtype=torch.int32, device=device)
+        self.local_inbox = torch.zeros(2 * 8 * n * 2, dtype=torch.int32, device=device)   # 8-byte pairs
+        self.epochs = torch.zeros(2 * self.ROWS, dtype=torch.int32, device=device)
         torch.cuda.synchronize(device)
-        mine = (reduce_tensor(self.local_sums), reduce_tensor(self.local_flags))
         everyone = [None] * tp.size
-        dist.all_gather_object(everyone, mine, group=tp.group)
-        self.sums, self.flags = [], []
+        dist.all_gather_object(everyone, reduce_tensor(self.local_inbox), group=tp.group)
+
         def open_on_my_device(reduced):
             # The handle is opened with THIS rank's device current, so the peer's memory is mapped into this
             # device's address space (the driver enables peer access for the mapping) - the arrangement NCCL's
@@ -71,19 +70,11 @@ class PeerBuffers:
             args[6] = device.index   # storage_device
             return fn(*args)
 
-        for r, (rs, rf) in enumerate(everyone):
-            if r == tp.rank:
-                self.sums.append(self.local_sums)
-                self.flags.append(self.local_flags)
-            else:
-                self.sums.append(open_on_my_device(rs))
-                self.flags.append(open_on_my_device(rf))
+        self.inboxes = [self.local_inbox if r == tp.rank else open_on_my_device(h) for r, h in enumerate(everyone)]
         torch.cuda.synchronize(device)
         dist.barrier(group=tp.group)
-        PtrArray = ctypes.c_void_p * tp.size
         self._n = n
-        self.sum_ptrs = [PtrArray(*[t.data_ptr() + 4 * n * b for t in self.sums]) for b in (0, 1)]
-        self.flag_ptrs = PtrArray(*[t.data_ptr() for t in self.flags])
+        self.inbox_ptrs = (ctypes.c_void_p * tp.size)(*[t.data_ptr() for t in self.inboxes])
 
     def buffer(self, which, rows):
         """This rank's partial-sum buffer 0 (attention output projection) or 1 (FFN down projection)."""

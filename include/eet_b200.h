@@ -145,17 +145,18 @@ int eet_rmsnorm_finalize(float* sums, const void* scale, const void* residual, v
 
 /*
  * Tensor-parallel form of eet_rmsnorm_finalize (decode, M <= 16): the all-reduce of a row-parallel projection
- * fused into the kernel that consumes it.  peer_sums[r] / peer_flags[r] (host arrays of `world` device
- * pointers, r = rank) address every rank's partial-sum buffer [M][n] fp32 and flag array (16 x 8 int32, zero
- * at start) in memory all ranks can reach (CUDA IPC / peer access); epochs: 16 int32 of this rank, zero at
- * start; zero_local: this rank's OTHER sum buffer, zeroed by this call (two buffers alternate between the
- * attention-output and FFN-down projections).  The rows' CTAs of all ranks meet at a flag barrier with a
- * bounded wait (status 4 in eet_device_status if a peer never arrives), add the partial rows in fp32 in rank
- * order, then scale, residual, RMSNorm as eet_rmsnorm_finalize.  The reference is single-GPU: no counterpart.
+ * fused into the kernel that consumes it.  local_sums: this rank's partial sums [M][n] fp32 (zeroed by the call).
+ * peer_inbox[r] (host array of `world` device pointers, r = rank): every rank's inbox, 2 * 8 * 16 * n pairs of
+ * {float bits, int32 epoch} (8 bytes each, zero at start), in memory all ranks can reach (CUDA IPC / peer
+ * access).  which: 0 or 1, the inbox of this exchange - consecutive exchanges must alternate.  epochs: 32 int32 of
+ * this rank, zero at start.  Each row's CTA pushes its partial row into every peer's inbox, then polls its own
+ * inbox - a bounded wait, status 4 in eet_device_status if a peer never arrives - and adds the partial rows in
+ * fp32 in rank order; then scale, residual, RMSNorm as eet_rmsnorm_finalize.  The reference is single-GPU: no
+ * counterpart.
  */
-int eet_rmsnorm_finalize_tp(const float* const* peer_sums, int* const* peer_flags, int world, int rank, int* epochs,
-                            float* zero_local, const void* scale, const void* residual, void* h_out, const void* gamma,
-                            void* xn_out, int M, int n, float eps, void* stream);
+int eet_rmsnorm_finalize_tp(float* local_sums, void* const* peer_inbox, int world, int rank, int which, int* epochs,
+                            const void* scale, const void* residual, void* h_out, const void* gamma, void* xn_out, int M,
+                            int n, float eps, void* stream);
 
 /* act_out = up * silu(gate) where gate = fp16(gate_sums * gate_scale), up = fp16(up_sums * up_scale) are the
  * unfinished products of eet_gemm_w8a16_accum; both sum buffers are zeroed.
