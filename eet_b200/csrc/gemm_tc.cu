@@ -212,15 +212,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t* __rest
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
         if (lane == 0) {
-            for (int kb = 0; kb < KT; ++kb) {
-                const int s = kb % kTcStages;
-                if (kb >= kTcStages && !tc_wait(&sm.empty[s], ((kb / kTcStages) - 1) & 1, &sm.abort)) break;
+            // (ring positions are counters: this loop is one thread's chain of dependent instructions)
+            int s = 0;
+            uint32_t ph = 1;
+            const uint8_t* w0 = Bw + (size_t)(n0 / kTile) * KT * kTileBytes;
+            for (int kb = 0; kb < KT; ++kb, w0 += kTileBytes) {
+                if (kb >= kTcStages && !tc_wait(&sm.empty[s], ph, &sm.abort)) break;
                 uint8_t* st = ring + (size_t)s * kStageBytes;
                 mbar_arrive_expect_tx(&sm.full[s], (uint32_t)(kTcW8Bytes + BN * 128));
-                const uint8_t* w0 = Bw + ((size_t)(n0 / kTile) * KT + kb) * kTileBytes;
                 bulk_g2s(st, w0, kTileBytes, &sm.full[s]);
                 bulk_g2s(st + kTileBytes, w0 + (size_t)KT * kTileBytes, kTileBytes, &sm.full[s]);
                 tma_load_2d(st + kTcW8Bytes + kTcWhBytes, &tmap_x, kb * kTile, m0, &sm.full[s]);
+                if (++s == kTcStages) {
+                    s = 0;
+                    ph ^= 1;
+                }
             }
         }
     }
@@ -228,21 +234,26 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t* __rest
         // ------------------------------------------------------------------ MMA issuer
         if (lane == 0) {
             constexpr uint32_t idesc = umma_idesc_f16(128, BN);
+            const uint64_t a_desc0 = umma_desc_sw128(smem_u32(ring + kTcW8Bytes));
+            const uint64_t b_desc0 = umma_desc_sw128(smem_u32(ring + kTcW8Bytes + kTcWhBytes));
+            int s = 0;
+            uint32_t ph = 0;
             for (int kb = 0; kb < KT; ++kb) {
-                const int s = kb % kTcStages;
-                const uint32_t ph = (kb / kTcStages) & 1;
                 if (!tc_wait(&sm.full[s], ph, &sm.abort)) break;    // activations landed
                 if (!tc_wait(&sm.ready[s], ph, &sm.abort)) break;   // fp16 weights written
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint8_t* st = ring + (size_t)s * kStageBytes;
-                const uint64_t a_desc = umma_desc_sw128(smem_u32(st + kTcW8Bytes));
-                const uint64_t b_desc = umma_desc_sw128(smem_u32(st + kTcW8Bytes + kTcWhBytes));
-#pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    // 16 reduction indices = 32 bytes along the swizzled row: +2 in 16-byte address units
-                    umma_f16(tmem, a_desc + (uint64_t)(2 * k), b_desc + (uint64_t)(2 * k), idesc, (kb | k) != 0);
-                }
+                const uint64_t a_desc = a_desc0 + (uint64_t)(s * (kStageBytes >> 4));
+                const uint64_t b_desc = b_desc0 + (uint64_t)(s * (kStageBytes >> 4));
+                // 16 reduction indices = 32 bytes along the swizzled row: +2 in 16-byte address units
+                umma_f16(tmem, a_desc, b_desc, idesc, kb != 0);
+                umma_f16(tmem, a_desc + 2, b_desc + 2, idesc, true);
+                umma_f16(tmem, a_desc + 4, b_desc + 4, idesc, true);
+                umma_f16(tmem, a_desc + 6, b_desc + 6, idesc, true);
                 umma_commit(&sm.empty[s]);
+                if (++s == kTcStages) {
+                    s = 0;
+                    ph ^= 1;
+                }
             }
             umma_commit(&sm.accum);
         }
@@ -250,9 +261,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t* __rest
     else {
         // ------------------------------------------------------------------ transform warps, then epilogue
         const int tw = threadIdx.x - 64;          // 0..127
+        int s = 0;
+        uint32_t ph = 0;
         for (int kb = 0; kb < KT; ++kb) {
-            const int s = kb % kTcStages;
-            const uint32_t ph = (kb / kTcStages) & 1;
             if (!tc_wait(&sm.full[s], ph, &sm.abort)) break;
             uint8_t* st = ring + (size_t)s * kStageBytes;
             const uint8_t* w8 = st;
@@ -275,6 +286,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t* __rest
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(&sm.ready[s]);
+            if (++s == kTcStages) {
+                s = 0;
+                ph ^= 1;
+            }
         }
 
         // ---- epilogue: TMEM lane = channel, columns = tokens ----
@@ -592,8 +607,8 @@ int launch_gemm_tc(const __half* A, const uint8_t* B, const __half* scale, __hal
                                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     EET_CHECK(rc == CUDA_SUCCESS, "tensor-core GEMM: cuTensorMapEncodeTiled failed with code %d", (int)rc);
-    // the 256 x 256 tiles pay off once there are enough of them to fill the machine more than once
-    if (N % 256 == 0 && (long long)(N / 256) * ((M + 255) / 256) >= 200) {
+    // the 256 x 256 tiles pay off once there are enough of them to fill most of the machine
+    if (N % 256 == 0 && (long long)(N / 256) * ((M + 255) / 256) >= 120) {
         static bool attr_set2[64] = {};
         int dev = 0;
         EET_CUDA(cudaGetDevice(&dev));

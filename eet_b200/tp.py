@@ -108,15 +108,17 @@ def head_range(num_heads, rank, size):
 
 
 def ff_range(d_ff, rank, size):
-    """FFN inner channels [lo, hi) owned by `rank`.  The packed weight layout works in tiles of 64
-    channels, so the split is by tiles and may be uneven: LLaMA-7B's 11008 = 172 tiles over 8 ranks gives
-    shards of 21 or 22 tiles."""
+    """FFN inner channels [lo, hi) owned by `rank`.  The tensor-core GEMMs work in strips of 128 output
+    channels (the packed layout in tiles of 64), so the split is by 128-channel strips when d_ff allows it,
+    else by 64-channel tiles, and may be uneven: LLaMA-7B's 11008 = 86 strips over 8 ranks gives shards of 10
+    or 11 strips."""
     if d_ff % 64:
         raise ValueError(f"d_ff {d_ff} must be a multiple of 64")
-    tiles = d_ff // 64
-    if tiles < size:
+    unit = 128 if d_ff % 128 == 0 and d_ff // 128 >= size else 64
+    units = d_ff // unit
+    if units < size:
         raise ValueError(f"d_ff {d_ff} has fewer 64-channel tiles than the {size} ranks")
-    return 64 * (tiles * rank // size), 64 * (tiles * (rank + 1) // size)
+    return unit * (units * rank // size), unit * (units * (rank + 1) // size)
 
 
 def shard_plan(num_heads, d_ff, size):

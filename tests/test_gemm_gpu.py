@@ -205,3 +205,20 @@ def test_stream_k_accumulate_two_weights_exact_sums(M):
         assert torch.equal(sums2.cpu().double(), rep * (x.double() @ q2.double()))
     from eet_b200 import _lib
     assert _lib.device_status() == 0
+
+
+@pytest.mark.parametrize("KNM", [(512, 384, 600), (1024, 640, 1000), (256, 4096, 2048), (4096, 4096, 1024)])
+def test_large_m_tensor_core_kernels(KNM):
+    """M > 512: the 256 x 256 tile kernel when N is a multiple of 256 and there are enough tiles, else the
+    128-channel x 256-token kernel; ragged last token tile, residual epilogue."""
+    K, N, M = KNM
+    x, q, s = _case(K, N, M, seed=K + N + M)
+    y = _run(x, q, s)
+    rows = torch.tensor([0, 1, 127, 128, 255, 256, 511, 512, M - 2, M - 1])
+    ref = ops.gemm_w8a16_fp32(x[rows], q, s)
+    assert ((y[rows].double() - ref).abs() <= 1e-2 * ref.abs().amax(1, keepdim=True)).all()
+    exact = ops.gemm_w8a16(x[rows], q, s, exact=True).double()
+    assert ((y[rows].double() - exact).abs() <= 2e-3 * ref.abs().amax(1, keepdim=True) + 1e-3).all()
+    res = torch.randn(M, N, generator=torch.Generator().manual_seed(2)).half()
+    yr = _run(x, q, s, residual=res)
+    assert torch.equal(yr[rows], ops.add_residual(y[rows], res[rows]))

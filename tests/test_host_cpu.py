@@ -43,10 +43,10 @@ def test_convert_name_rules():
 def test_shard_plan():
     plan = tp.shard_plan(32, 11008, 2)
     assert plan == [((0, 16), (0, 5504)), ((16, 32), (5504, 11008))]
-    # 172 tiles of 64 over 8 ranks: uneven, contiguous, complete
+    # 86 strips of 128 over 8 ranks: uneven, contiguous, complete
     plan8 = tp.shard_plan(32, 11008, 8)
     widths = [hi - lo for _, (lo, hi) in plan8]
-    assert sum(widths) == 11008 and set(widths) == {21 * 64, 22 * 64}
+    assert sum(widths) == 11008 and set(widths) == {10 * 128, 11 * 128}
     assert all(plan8[i][1][1] == plan8[i + 1][1][0] for i in range(7))
     with pytest.raises(ValueError):
         tp.shard_plan(32, 11008, 3)     # heads do not divide
