@@ -4,6 +4,8 @@
 //
 // Each mirrors the arithmetic of a reference kernel (cited per function) and is sized for HBM:
 // 16-byte accesses, one pass over the data where the reference makes two.
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 #include "kernels.h"
 
@@ -217,102 +219,99 @@ __device__ __forceinline__ uint4 ld_volatile_u4(const void* p)
     return v;
 }
 
+// One row is split over the CTAs of a thread-block cluster (up to 8): the peer stores of a row leave from
+// up to 8 SMs instead of one (what one SM can push over NVLink per microsecond bounded the exchange at 4 and 8
+// ranks), and the row's sum of squares meets through distributed shared memory.  One 8-float vector per thread.
 __global__ void __launch_bounds__(1024)
 rmsnorm_finalize_tp_kernel(TpPeers peers, float* __restrict__ local_sums, int* __restrict__ epochs,
                            const __half* __restrict__ scale, const __half* __restrict__ residual,
                            __half* __restrict__ h_out, const __half* __restrict__ gamma, __half* __restrict__ xn_out,
                            int n, float eps)
 {
+    namespace cgx = cooperative_groups;
+    cgx::cluster_group cluster = cgx::this_cluster();
     __shared__ float red[32];
-    __shared__ float s_inv;
+    __shared__ float s_part;     // this CTA's share of the row's sum of squares, read by the cluster
     __shared__ int s_epoch;
     pdl_launch_dependents();
     pdl_wait();   // this rank's GEMM (and everything before it) is complete
-    const int row = blockIdx.x;
-    if (threadIdx.x == 0) {
-        s_epoch = epochs[peers.which * kTpRows + row] + 1;
-        epochs[peers.which * kTpRows + row] = s_epoch;
-    }
+    const int slices = (int)cluster.num_blocks();
+    const int slice = (int)cluster.block_rank();
+    const int row = blockIdx.x / slices;
+    // every CTA of the row derives the epoch from the counter; the row's first CTA advances it afterwards
+    if (threadIdx.x == 0) s_epoch = epochs[peers.which * kTpRows + row] + 1;
     __syncthreads();
     const uint32_t epoch = (uint32_t)s_epoch;
-    const int nv = n >> 3;
     const size_t slot_row = (size_t)(peers.which * 8) * kTpRows * n + (size_t)row * n;   // + src * kTpRows * n
+    const int i = slice * blockDim.x + threadIdx.x;   // this thread's vector of 8 columns
 
     // ---- push this rank's partial row to every peer, keep a copy, zero the local sums for the next GEMM ----
-    float mine[2][8];
+    float mine[8];
+    {
+        float4* lp = reinterpret_cast<float4*>(local_sums + (size_t)row * n + (size_t)i * 8);
+        const float4 a = lp[0], b = lp[1];
+        mine[0] = a.x; mine[1] = a.y; mine[2] = a.z; mine[3] = a.w;
+        mine[4] = b.x; mine[5] = b.y; mine[6] = b.z; mine[7] = b.w;
+        const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+        lp[0] = z;
+        lp[1] = z;
 #pragma unroll
-    for (int j = 0; j < 2; ++j) {
-        const int i = threadIdx.x + j * blockDim.x;
-        if (i < nv) {
-            float4* lp = reinterpret_cast<float4*>(local_sums + (size_t)row * n + (size_t)i * 8);
-            const float4 a = lp[0], b = lp[1];
-            mine[j][0] = a.x; mine[j][1] = a.y; mine[j][2] = a.z; mine[j][3] = a.w;
-            mine[j][4] = b.x; mine[j][5] = b.y; mine[j][6] = b.z; mine[j][7] = b.w;
-            const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
-            lp[0] = z;
-            lp[1] = z;
-            for (int p = 0; p < peers.world; ++p) {
-                if (p == peers.rank) continue;
+        for (int p = 0; p < 8; ++p) {
+            if (p < peers.world && p != peers.rank) {
                 uint4* dst = reinterpret_cast<uint4*>(peers.inbox[p] + slot_row + (size_t)peers.rank * kTpRows * n +
                                                       (size_t)i * 8);
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
-                    dst[e] = make_uint4(__float_as_uint(mine[j][2 * e]), epoch, __float_as_uint(mine[j][2 * e + 1]), epoch);
+                    dst[e] = make_uint4(__float_as_uint(mine[2 * e]), epoch, __float_as_uint(mine[2 * e + 1]), epoch);
                 }
             }
         }
     }
 
     // ---- collect: poll the local inbox until every peer's pairs carry this epoch, add in rank order ----
-    const uint4* rr = reinterpret_cast<const uint4*>(residual + (size_t)row * n);
-    uint4 h[2];
-    float ss = 0.f;
+    float v[8];
 #pragma unroll
-    for (int j = 0; j < 2; ++j) {
-        const int i = threadIdx.x + j * blockDim.x;
-        if (i < nv) {
-            float v[8];
+    for (int e = 0; e < 8; ++e) v[e] = 0.f;
 #pragma unroll
-            for (int e = 0; e < 8; ++e) v[e] = 0.f;
-            for (int r = 0; r < peers.world; ++r) {
-                if (r == peers.rank) {
+    for (int r = 0; r < 8; ++r) {
+        if (r >= peers.world) continue;
+        if (r == peers.rank) {
 #pragma unroll
-                    for (int e = 0; e < 8; ++e) v[e] += mine[j][e];
-                    continue;
-                }
-                const uint4* src = reinterpret_cast<const uint4*>(peers.inbox[peers.rank] + slot_row +
-                                                                  (size_t)r * kTpRows * n + (size_t)i * 8);
-                uint4 c[4];
-                uint32_t spins = 0;
-                while (true) {
+            for (int e = 0; e < 8; ++e) v[e] += mine[e];
+            continue;
+        }
+        const uint4* src = reinterpret_cast<const uint4*>(peers.inbox[peers.rank] + slot_row + (size_t)r * kTpRows * n +
+                                                          (size_t)i * 8);
+        uint4 c[4];
+        uint32_t spins = 0;
+        while (true) {
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) c[e] = ld_volatile_u4(src + e);
-                    bool ok = true;
+            for (int e = 0; e < 4; ++e) c[e] = ld_volatile_u4(src + e);
+            bool ok = true;
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) ok = ok && c[e].y == epoch && c[e].w == epoch;
-                    if (ok) break;
-                    if (++spins > kTpSpinLimit) {
-                        g_device_status = 4;   // a peer never arrived: give up, the host reads the status word
-                        break;
-                    }
-                }
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    v[2 * e] += __uint_as_float(c[e].x);
-                    v[2 * e + 1] += __uint_as_float(c[e].z);
-                }
-            }
-            h[j] = rr[i];
-            const uint4 sc = reinterpret_cast<const uint4*>(scale)[i];
-            h[j] = finalize8(v, sc, &h[j]);
-            reinterpret_cast<uint4*>(h_out + (size_t)row * n)[i] = h[j];
-            const __half2* hh = reinterpret_cast<const __half2*>(&h[j]);
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const float2 f = __half22float2(hh[e]);
-                ss += f.x * f.x + f.y * f.y;
+            for (int e = 0; e < 4; ++e) ok = ok && c[e].y == epoch && c[e].w == epoch;
+            if (ok) break;
+            if (++spins > kTpSpinLimit) {
+                g_device_status = 4;   // a peer never arrived: give up, the host reads the status word
+                break;
             }
         }
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            v[2 * e] += __uint_as_float(c[e].x);
+            v[2 * e + 1] += __uint_as_float(c[e].z);
+        }
+    }
+    uint4 h = reinterpret_cast<const uint4*>(residual + (size_t)row * n)[i];
+    const uint4 sc = reinterpret_cast<const uint4*>(scale)[i];
+    h = finalize8(v, sc, &h);
+    reinterpret_cast<uint4*>(h_out + (size_t)row * n)[i] = h;
+    float ss = 0.f;
+    const __half2* hh = reinterpret_cast<const __half2*>(&h);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        const float2 f = __half22float2(hh[e]);
+        ss += f.x * f.x + f.y * f.y;
     }
     ss = warp_sum(ss);
     if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
@@ -320,28 +319,27 @@ rmsnorm_finalize_tp_kernel(TpPeers peers, float* __restrict__ local_sums, int* _
     if (threadIdx.x < 32) {
         float t = (threadIdx.x < (blockDim.x >> 5)) ? red[threadIdx.x] : 0.f;
         t = warp_sum(t);
-        if (threadIdx.x == 0) s_inv = rsqrtf(t / n + eps);
+        if (threadIdx.x == 0) s_part = t;
     }
-    __syncthreads();
-    const float inv = s_inv;
+    cluster.sync();   // every CTA's share is written (and every CTA has read the old epoch counter)
+    float total = 0.f;
+    for (int c = 0; c < slices; ++c) total += *cluster.map_shared_rank(&s_part, c);   // same order in every CTA
+    if (slice == 0 && threadIdx.x == 0) epochs[peers.which * kTpRows + row] = (int)epoch;
+    const float inv = rsqrtf(total / n + eps);
+    {
+        const uint4 g = reinterpret_cast<const uint4*>(gamma)[i];
+        const __half2* gh = reinterpret_cast<const __half2*>(&g);
+        uint4 o;
+        __half2* oh = reinterpret_cast<__half2*>(&o);
 #pragma unroll
-    for (int j = 0; j < 2; ++j) {
-        const int i = threadIdx.x + j * blockDim.x;
-        if (i < nv) {
-            const uint4 g = reinterpret_cast<const uint4*>(gamma)[i];
-            const __half2* hh = reinterpret_cast<const __half2*>(&h[j]);
-            const __half2* gh = reinterpret_cast<const __half2*>(&g);
-            uint4 o;
-            __half2* oh = reinterpret_cast<__half2*>(&o);
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const float2 f = __half22float2(hh[e]);
-                const float2 gg = __half22float2(gh[e]);
-                oh[e] = __float22half2_rn(make_float2(f.x * inv * gg.x, f.y * inv * gg.y));
-            }
-            reinterpret_cast<uint4*>(xn_out + (size_t)row * n)[i] = o;
+        for (int e = 0; e < 4; ++e) {
+            const float2 f = __half22float2(hh[e]);
+            const float2 gg = __half22float2(gh[e]);
+            oh[e] = __float22half2_rn(make_float2(f.x * inv * gg.x, f.y * inv * gg.y));
         }
+        reinterpret_cast<uint4*>(xn_out + (size_t)row * n)[i] = o;
     }
+    cluster.sync();   // no CTA leaves while its shared memory may still be read by the others
 }
 
 // gate <- up * gate / (1 + exp(-gate)) with the reference's mix of precisions: exp in fp32 rounded to
@@ -553,12 +551,27 @@ int launch_rmsnorm_finalize_tp(float* local_sums, void* const* peer_inbox, int w
     peers.world = world;
     peers.rank = rank;
     peers.which = which;
+    // the row is split over the largest cluster (8, 4, 2 or 1 CTAs) that leaves every CTA whole warps
     const int nv = n / 8;
-    int threads = ((nv + 1) / 2 + 31) / 32 * 32;
-    if (threads < 32) threads = 32;
-    if (threads > 1024) threads = 1024;
-    EET_CUDA(launch_pdl(rmsnorm_finalize_tp_kernel, dim3(M), dim3(threads), 0, stream, peers, local_sums, epochs, scale,
-                        residual, h_out, gamma, xn_out, n, eps));
+    int slices = 8;
+    while (slices > 1 && (nv % (slices * 32) != 0 || nv / slices > 1024)) slices >>= 1;
+    EET_CHECK(nv % slices == 0 && nv / slices <= 1024, "tensor-parallel rmsnorm: hidden size %d is not supported", n);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(M * slices));
+    cfg.blockDim = dim3((unsigned)(nv / slices));
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)slices;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 2;
+    EET_CUDA(cudaLaunchKernelEx(&cfg, rmsnorm_finalize_tp_kernel, peers, local_sums, epochs, scale, residual, h_out, gamma,
+                                xn_out, n, eps));
     return 0;
 }
 
