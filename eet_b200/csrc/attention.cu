@@ -615,6 +615,9 @@ int launch_decode_mha(const DecodeAttnArgs& a, cudaStream_t stream)
         const int room = kAttnCtasPerSm * sm_count() / (a.B * a.H);
         splits = 1;
         while (splits < 8 && splits * 2 <= room && len / (splits * 2) >= 64) splits *= 2;
+        // more (batch, head) pairs than CTA slots: the launch runs in waves, and for long histories halves
+        // balance the last wave better (measured at 1024 pairs: +13 % at 1060 steps, -10 % at 320)
+        if (room == 0 && len >= 768) splits = 2;
     }
     EET_CHECK(splits == 1 || splits == 2 || splits == 4 || splits == 8, "decode attention: splits must be 1,2,4,8");
     cudaLaunchConfig_t cfg = {};
