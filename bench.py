@@ -165,11 +165,17 @@ def rewind(model, step):
         layer.attention.step_ = step
 
 
-def kernel_launches_per_step(n_layers):
-    # (with tensor parallelism two NCCL all-reduce kernels per layer come on top; they are not counted)
-    # per layer: rmsnorm(+finalize), qkv gemm, decode attention, out gemm, rmsnorm(+finalize), gate+up gemm,
-    # swiglu(+finalize), down gemm; per step: advance_steps + final rmsnorm(+finalize)
-    return 8 * n_layers + 2
+def kernel_launches_per_step(n_layers, batch, world):
+    """Launches of this library's kernels in one decode step (NCCL and torch kernels are not counted)."""
+    deferred_max = 16 if world > 1 else 64
+    if batch <= deferred_max:
+        # per layer: rmsnorm(+finalize), qkv gemm, decode attention, out gemm, rmsnorm(+finalize), gate+up gemm,
+        # swiglu(+finalize), down gemm; per step: advance_steps + final rmsnorm(+finalize)
+        return 8 * n_layers + 2
+    # larger batches: every projection is an accumulate + finalize pair, gate and up are separate launches
+    # (and with tensor parallelism the residual is added by its own kernel after the NCCL all-reduce)
+    per_layer = 14 + (2 if world > 1 else 0)
+    return per_layer * n_layers + 2
 
 
 # ------------------------------------------------------------------------------------------------ GEMM timing
@@ -418,7 +424,7 @@ def run_ours(args):
                     "d2h_bytes_per_step": BATCH * 8, "ms_per_step": round(t_e2e / K * 1e3, 4)},
             "prefill": None if prefill_ms is None else {"ms": round(prefill_ms, 2), "tokens": BATCH * PROMPT,
                                                          "tokens_per_s": round(BATCH * PROMPT / prefill_ms * 1e3)},
-            "gpu_launches": kernel_launches_per_step(n_layers) * K,
+            "gpu_launches": kernel_launches_per_step(n_layers, BATCH, world) * K,
             "clocks": clk.summary(), "clocks_e2e": clk_e2e.summary(), "device_status": status,
             "roofline": {"bound": "hbm",
                          "kernel": f"gemm_skinny_kernel<{1 if BATCH <= 8 else 2}>, fused QKV projection "

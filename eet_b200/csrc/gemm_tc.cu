@@ -140,13 +140,14 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32])
 // barrier per block is enough.  Called by all 128 epilogue threads.
 constexpr int kEpiStageHalves = 32 * 128;
 
+template<int kBarId = 1>
 __device__ __forceinline__ void epilogue_block(const uint32_t (&v)[32], float sc, __half* stage, int channel, int tw,
                                                __half* C, const __half* residual, int m_first, int M, int N,
                                                int n_first)
 {
 #pragma unroll
     for (int j = 0; j < 32; ++j) stage[j * 128 + channel] = __float2half(__uint_as_float(v[j]) * sc);
-    asm volatile("bar.sync 1, 128;" ::: "memory");
+    asm volatile("bar.sync %0, 128;" ::"n"(kBarId) : "memory");
     uint4 res[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
@@ -328,7 +329,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t* __rest
 //   int8 weights: 4 x 16 KiB, four 4 KiB bulk copies per k-block      (warp 6)
 //   fp16 weights: 3 x 16 KiB units of 128 channels x 64 k, written by warps 2-5, read by tcgen05.mma
 // ---------------------------------------------------------------------------------------------------
-constexpr int kTc2Threads = 224;
+constexpr int kTc2Threads = 352;   // X producer, MMA issuer, 4 + 4 transform/epilogue warps, W producer
 constexpr int kTc2NX = 3, kTc2NW = 4, kTc2NH = 3;
 constexpr int kTc2XBytes = 256 * 128, kTc2WBytes = 4 * kTileBytes, kTc2HBytes = 128 * 128;
 constexpr int kTc2Smem = kTc2NX * kTc2XBytes + kTc2NW * kTc2WBytes + kTc2NH * kTc2HBytes;
@@ -364,7 +365,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t* __res
         }
         for (int s = 0; s < kTc2NW; ++s) {
             mbar_init(&sm.w_full[s], 1);
-            mbar_init(&sm.w_empty[s], 4);
+            mbar_init(&sm.w_empty[s], 8);
         }
         for (int s = 0; s < kTc2NH; ++s) {
             mbar_init(&sm.h_ready[s], 4);
@@ -465,46 +466,41 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t* __res
     }
     else {
         // ------------------------------------------------------------------ transform warps, then epilogue
-        const int tw = threadIdx.x - 64;  // 0..127
-        bool ok = true;
-        int sw = 0, su = 0, filled = 0;
-        uint32_t phw = 0, phu = 1;
-        for (int kb = 0; kb < KT && ok; ++kb) {
+        // Two groups of four warps (2-5 and 7-10); group g owns the 128-channel half g of the tile: it converts
+        // that half of every k-block and later runs that accumulator's epilogue.  One group alone could not
+        // convert a k-block in the time the tensor core needs for it.  (A group never waits on a barrier
+        // phase it could be two completions ahead of: the unit it waits for, u - 3, precedes the unit u - 5
+        // whose completion let it write u - 2... in MMA order, which completes in order.)
+        const int grp = (warp >= 7) ? 1 : 0;
+        const int tw = (warp - (grp ? 7 : 2)) * 32 + lane;  // 0..127 within the group
+        int sw = 0;
+        uint32_t phw = 0;
+        for (int kb = 0; kb < KT; ++kb) {
             if (!tc_wait(&sm.w_full[sw], phw, &sm.abort)) break;
             const uint8_t* w8 = w_ring + (size_t)sw * kTc2WBytes;
-#pragma unroll 1
-            for (int h = 0; h < 2; ++h) {
-                if (filled >= kTc2NH && !tc_wait(&sm.h_empty[su], phu, &sm.abort)) {
-                    ok = false;
-                    break;
-                }
-                uint8_t* wh = h_ring + (size_t)su * kTc2HBytes;
+            const int u = 2 * kb + grp;            // unit = (k-block, half); h ring slot u % NH, use u / NH
+            const int su = u % kTc2NH, use = u / kTc2NH;
+            if (use >= 1 && !tc_wait(&sm.h_empty[su], (uint32_t)((use - 1) & 1), &sm.abort)) break;
+            uint8_t* wh = h_ring + (size_t)su * kTc2HBytes;
 #pragma unroll
-                for (int pass = 0; pass < 4; ++pass) {
-                    const int r = pass * 32 + (tw >> 2);   // channel row of this half, 0..127
-                    const int qd = tw & 3;
-                    const uint4 raw = *reinterpret_cast<const uint4*>(w8 + (h * 128 + r) * 64 + qd * 16);
-                    uint4 o0, o1;
-                    cvt_u8x4_to_f16x4(raw.x, o0.x, o0.y);
-                    cvt_u8x4_to_f16x4(raw.y, o0.z, o0.w);
-                    cvt_u8x4_to_f16x4(raw.z, o1.x, o1.y);
-                    cvt_u8x4_to_f16x4(raw.w, o1.z, o1.w);
-                    uint8_t* row = wh + r * 128;
-                    *reinterpret_cast<uint4*>(row + (((2 * qd) ^ (r & 7)) << 4)) = o0;
-                    *reinterpret_cast<uint4*>(row + (((2 * qd + 1) ^ (r & 7)) << 4)) = o1;
-                }
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&sm.h_ready[su]);
-                ++filled;
-                if (++su == kTc2NH) {
-                    su = 0;
-                    phu ^= 1;
-                }
+            for (int pass = 0; pass < 4; ++pass) {
+                const int r = pass * 32 + (tw >> 2);   // channel row of this half, 0..127
+                const int qd = tw & 3;
+                const uint4 raw = *reinterpret_cast<const uint4*>(w8 + (grp * 128 + r) * 64 + qd * 16);
+                uint4 o0, o1;
+                cvt_u8x4_to_f16x4(raw.x, o0.x, o0.y);
+                cvt_u8x4_to_f16x4(raw.y, o0.z, o0.w);
+                cvt_u8x4_to_f16x4(raw.z, o1.x, o1.y);
+                cvt_u8x4_to_f16x4(raw.w, o1.z, o1.w);
+                uint8_t* row = wh + r * 128;
+                *reinterpret_cast<uint4*>(row + (((2 * qd) ^ (r & 7)) << 4)) = o0;
+                *reinterpret_cast<uint4*>(row + (((2 * qd + 1) ^ (r & 7)) << 4)) = o1;
             }
-            if (ok) {
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&sm.w_empty[sw]);
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(&sm.h_ready[su]);
+                mbar_arrive(&sm.w_empty[sw]);
             }
             if (++sw == kTc2NW) {
                 sw = 0;
@@ -512,25 +508,33 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t* __res
             }
         }
 
-        // ---- epilogue: TMEM lane = channel within the half, columns = tokens ----
+        // ---- epilogue: TMEM lane = channel within the half, columns = tokens; group g takes accumulator g ----
         // every epilogue warp gets here (the waits are bounded); the barrier makes the abort decision uniform
         tc_wait(&sm.accum, 0, &sm.abort);
-        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (grp == 0) {
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+        }
+        else {
+            asm volatile("bar.sync 2, 128;" ::: "memory");
+        }
         if (sm.abort == 0) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const int lane_base = (warp & 3) * 32;
-            __half* stage = reinterpret_cast<__half*>(x_ring);
+            __half* stage = reinterpret_cast<__half*>(x_ring) + grp * 2 * kEpiStageHalves;
+            const float sc = __half2float(scale[n0 + grp * 128 + lane_base + lane]);
             int blk = 0;
 #pragma unroll 1
-            for (int h = 0; h < 2; ++h) {
-                const float sc = __half2float(scale[n0 + h * 128 + lane_base + lane]);
-#pragma unroll 1
-                for (int c0 = 0; c0 < 256; c0 += 32, ++blk) {
-                    if (m0 + c0 >= M) break;
-                    uint32_t v[32];
-                    tmem_ld32(tmem + ((uint32_t)lane_base << 16) + (uint32_t)(h * 256 + c0), v);
-                    epilogue_block(v, sc, stage + (blk & 1) * kEpiStageHalves, lane_base + lane, tw, C, residual, m0 + c0,
-                                   M, N, n0 + h * 128);
+            for (int c0 = 0; c0 < 256; c0 += 32, ++blk) {
+                if (m0 + c0 >= M) break;
+                uint32_t v[32];
+                tmem_ld32(tmem + ((uint32_t)lane_base << 16) + (uint32_t)(grp * 256 + c0), v);
+                if (grp == 0) {
+                    epilogue_block<1>(v, sc, stage + (blk & 1) * kEpiStageHalves, lane_base + lane, tw, C, residual, m0 + c0,
+                                      M, N, n0);
+                }
+                else {
+                    epilogue_block<2>(v, sc, stage + (blk & 1) * kEpiStageHalves, lane_base + lane, tw, C, residual, m0 + c0,
+                                      M, N, n0 + 128);
                 }
             }
         }

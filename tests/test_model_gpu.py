@@ -186,3 +186,28 @@ def test_embedding_op():
     normed = emb.forward_transformers(ids, pid, tid, True)
     ref = torch.nn.functional.layer_norm(want.float(), (h,), eps=desc.layernorm_eps).half()
     assert torch.allclose(normed.float(), ref.float(), atol=2e-3)
+
+
+def test_decode_batch_above_16_uses_the_stream_k_kernel_and_matches_oracle():
+    """Batches of 17..64 sequences keep the deferred-epilogue decode chain, with the projections on the
+    stream-K tensor-core kernel: eager logits against the oracle, and graph replay equal to eager tokens."""
+    cfg = tiny_config()
+    sd = random_hf_state_dict(cfg, seed=17)
+    B, S, NEW, T = 20, 3, 4, 10
+    model = _build(cfg, sd, "EETLlamaForCausalLM", "convert_llama_weights", B, 4, T)
+    lm = OracleLM(sd, cfg, max_len=T, batch=B)
+    gen = torch.Generator().manual_seed(18)
+    ids = torch.randint(0, cfg.vocab_size, (B, S + NEW), generator=gen)
+    assert _logits_close(model(ids[:, :S].cuda(), first_pass=True).logits, lm(ids[:, :S], True))
+    from eet_b200 import EET
+    for t in range(S, S + 2):
+        with EET.deferred_epilogue():   # what decode_step does: epilogues finished by the next op
+            hidden = model.model(input_ids=ids[:, t:t + 1].cuda(), first_pass=False)
+        logits = model.lm_head(hidden)
+        assert _logits_close(logits, lm(ids[:, t:t + 1], False)), f"decode step {t}"
+    eager = model.generate(ids[:, :S].cuda(), NEW).cpu()
+    model.use_cuda_graph = True
+    graphed = model.generate(ids[:, :S].cuda(), NEW).cpu()
+    assert torch.equal(eager, graphed)
+    from eet_b200 import _lib
+    assert _lib.device_status() == 0
