@@ -327,17 +327,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t* __rest
 // so that each can run as far ahead as its buffer allows:
 //   activations : 3 x 32 KiB, one 2-D TMA copy per k-block            (warp 0)
 //   int8 weights: 4 x 16 KiB, four 4 KiB bulk copies per k-block      (warp 6)
-//   fp16 weights: 3 x 16 KiB units of 128 channels x 64 k, written by warps 2-5, read by tcgen05.mma
+//   fp16 weights: 2 x 32 KiB (k-block x two 128-channel halves), written by warps 2-5 / 7-10, read by tcgen05.mma
+// One commit per k-block ("done", ring of 6 = lcm of the ring depths) releases the activation stage to its
+// producer and the fp16 stage to the transform warps: the issuing thread pays for two waits, eight MMAs and
+// one commit per k-block.
 // ---------------------------------------------------------------------------------------------------
 constexpr int kTc2Threads = 352;   // X producer, MMA issuer, 4 + 4 transform/epilogue warps, W producer
-constexpr int kTc2NX = 3, kTc2NW = 4, kTc2NH = 3;
-constexpr int kTc2XBytes = 256 * 128, kTc2WBytes = 4 * kTileBytes, kTc2HBytes = 128 * 128;
-constexpr int kTc2Smem = kTc2NX * kTc2XBytes + kTc2NW * kTc2WBytes + kTc2NH * kTc2HBytes;
+constexpr int kTc2NX = 3, kTc2NW = 4, kTc2NH = 2, kTc2ND = 6;
+constexpr int kTc2XBytes = 256 * 128, kTc2WBytes = 4 * kTileBytes, kTc2HBytes = 128 * 128;   // H: one half
+constexpr int kTc2Smem = kTc2NX * kTc2XBytes + kTc2NW * kTc2WBytes + kTc2NH * 2 * kTc2HBytes;
 
 struct Tc2Smem {
-    uint64_t x_full[kTc2NX], x_empty[kTc2NX];
+    uint64_t x_full[kTc2NX];
     uint64_t w_full[kTc2NW], w_empty[kTc2NW];
-    uint64_t h_ready[kTc2NH], h_empty[kTc2NH];
+    uint64_t h_ready[kTc2NH];     // both halves of a k-block are written (8 transform warps)
+    uint64_t done[kTc2ND];        // the MMAs of a k-block have completed
     uint64_t accum;
     uint32_t tmem_base;
     volatile int abort;
@@ -352,25 +356,20 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t* __res
     uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(tc_dyn) + 1023) & ~(uintptr_t)1023);
     uint8_t* x_ring = base;                                   // 1024-byte aligned tiles (swizzled)
     uint8_t* h_ring = base + kTc2NX * kTc2XBytes;             // 1024-byte aligned tiles (swizzled)
-    uint8_t* w_ring = h_ring + kTc2NH * kTc2HBytes;
+    uint8_t* w_ring = h_ring + kTc2NH * 2 * kTc2HBytes;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n0 = blockIdx.x * 256;
     const int m0 = blockIdx.y * 256;
     const int KT = K / kTile;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kTc2NX; ++s) {
-            mbar_init(&sm.x_full[s], 1);
-            mbar_init(&sm.x_empty[s], 1);
-        }
+        for (int s = 0; s < kTc2NX; ++s) mbar_init(&sm.x_full[s], 1);
+        for (int s = 0; s < kTc2ND; ++s) mbar_init(&sm.done[s], 1);
         for (int s = 0; s < kTc2NW; ++s) {
             mbar_init(&sm.w_full[s], 1);
             mbar_init(&sm.w_empty[s], 8);
         }
-        for (int s = 0; s < kTc2NH; ++s) {
-            mbar_init(&sm.h_ready[s], 4);
-            mbar_init(&sm.h_empty[s], 1);
-        }
+        for (int s = 0; s < kTc2NH; ++s) mbar_init(&sm.h_ready[s], 8);
         mbar_init(&sm.accum, 1);
         sm.abort = 0;
         mbar_fence_init();
@@ -390,16 +389,19 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t* __res
         // ------------------------------------------------------------------ activation producer
         if (lane == 0) {
             // (ring positions are counters: this loop is one thread's chain of dependent instructions)
-            int s = 0;
-            uint32_t ph = 1;
+            int s = 0, d = 0;      // d: slot of done[] for k-block kb - NX
+            uint32_t phd = 0;
             for (int kb = 0; kb < KT; ++kb) {
-                if (kb >= kTc2NX && !tc_wait(&sm.x_empty[s], ph, &sm.abort)) break;
+                if (kb >= kTc2NX) {
+                    if (!tc_wait(&sm.done[d], phd, &sm.abort)) break;
+                    if (++d == kTc2ND) {
+                        d = 0;
+                        phd ^= 1;
+                    }
+                }
                 mbar_arrive_expect_tx(&sm.x_full[s], (uint32_t)kTc2XBytes);
                 tma_load_2d(x_ring + (size_t)s * kTc2XBytes, &tmap_x, kb * kTile, m0, &sm.x_full[s]);
-                if (++s == kTc2NX) {
-                    s = 0;
-                    ph ^= 1;
-                }
+                if (++s == kTc2NX) s = 0;
             }
         }
     }
@@ -430,32 +432,26 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t* __res
             constexpr uint32_t idesc = umma_idesc_f16(128, 256);
             const uint64_t b_desc0 = umma_desc_sw128(smem_u32(x_ring));
             const uint64_t a_desc0 = umma_desc_sw128(smem_u32(h_ring));
-            int sx = 0, su = 0;
-            uint32_t phx = 0, phu = 0;
-            bool ok = true;
-            for (int kb = 0; kb < KT && ok; ++kb) {
+            int sx = 0, sd = 0;
+            uint32_t phx = 0;
+            for (int kb = 0; kb < KT; ++kb) {
+                const int sh = kb & 1;
                 if (!tc_wait(&sm.x_full[sx], phx, &sm.abort)) break;
+                if (!tc_wait(&sm.h_ready[sh], (uint32_t)((kb >> 1) & 1), &sm.abort)) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint64_t b_desc = b_desc0 + (uint64_t)(sx * (kTc2XBytes >> 4));
-#pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    if (!tc_wait(&sm.h_ready[su], phu, &sm.abort)) {
-                        ok = false;
-                        break;
-                    }
-                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const uint64_t a_desc = a_desc0 + (uint64_t)(su * (kTc2HBytes >> 4));
-                    const uint32_t d = tmem + (uint32_t)(h * 256);
-                    umma_f16(d, a_desc, b_desc, idesc, kb != 0);
-                    umma_f16(d, a_desc + 2, b_desc + 2, idesc, true);
-                    umma_f16(d, a_desc + 4, b_desc + 4, idesc, true);
-                    umma_f16(d, a_desc + 6, b_desc + 6, idesc, true);
-                    umma_commit(&sm.h_empty[su]);
-                    if (++su == kTc2NH) {
-                        su = 0;
-                        phu ^= 1;
-                    }
-                }
-                if (ok) umma_commit(&sm.x_empty[sx]);
+                const uint64_t a0 = a_desc0 + (uint64_t)(sh * (2 * kTc2HBytes >> 4));
+                const uint64_t a1 = a0 + (uint64_t)(kTc2HBytes >> 4);
+                umma_f16(tmem, a0, b_desc, idesc, kb != 0);
+                umma_f16(tmem, a0 + 2, b_desc + 2, idesc, true);
+                umma_f16(tmem, a0 + 4, b_desc + 4, idesc, true);
+                umma_f16(tmem, a0 + 6, b_desc + 6, idesc, true);
+                umma_f16(tmem + 256, a1, b_desc, idesc, kb != 0);
+                umma_f16(tmem + 256, a1 + 2, b_desc + 2, idesc, true);
+                umma_f16(tmem + 256, a1 + 4, b_desc + 4, idesc, true);
+                umma_f16(tmem + 256, a1 + 6, b_desc + 6, idesc, true);
+                umma_commit(&sm.done[sd]);
+                if (++sd == kTc2ND) sd = 0;
                 if (++sx == kTc2NX) {
                     sx = 0;
                     phx ^= 1;
@@ -468,20 +464,23 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t* __res
         // ------------------------------------------------------------------ transform warps, then epilogue
         // Two groups of four warps (2-5 and 7-10); group g owns the 128-channel half g of the tile: it converts
         // that half of every k-block and later runs that accumulator's epilogue.  One group alone could not
-        // convert a k-block in the time the tensor core needs for it.  (A group never waits on a barrier
-        // phase it could be two completions ahead of: the unit it waits for, u - 3, precedes the unit u - 5
-        // whose completion let it write u - 2... in MMA order, which completes in order.)
+        // convert a k-block in the time the tensor core needs for it.
         const int grp = (warp >= 7) ? 1 : 0;
         const int tw = (warp - (grp ? 7 : 2)) * 32 + lane;  // 0..127 within the group
-        int sw = 0;
-        uint32_t phw = 0;
+        int sw = 0, d = 0;     // d: slot of done[] for k-block kb - NH
+        uint32_t phw = 0, phd = 0;
         for (int kb = 0; kb < KT; ++kb) {
             if (!tc_wait(&sm.w_full[sw], phw, &sm.abort)) break;
             const uint8_t* w8 = w_ring + (size_t)sw * kTc2WBytes;
-            const int u = 2 * kb + grp;            // unit = (k-block, half); h ring slot u % NH, use u / NH
-            const int su = u % kTc2NH, use = u / kTc2NH;
-            if (use >= 1 && !tc_wait(&sm.h_empty[su], (uint32_t)((use - 1) & 1), &sm.abort)) break;
-            uint8_t* wh = h_ring + (size_t)su * kTc2HBytes;
+            const int sh = kb & 1;
+            if (kb >= kTc2NH) {
+                if (!tc_wait(&sm.done[d], phd, &sm.abort)) break;
+                if (++d == kTc2ND) {
+                    d = 0;
+                    phd ^= 1;
+                }
+            }
+            uint8_t* wh = h_ring + (size_t)(sh * 2 + grp) * kTc2HBytes;
 #pragma unroll
             for (int pass = 0; pass < 4; ++pass) {
                 const int r = pass * 32 + (tw >> 2);   // channel row of this half, 0..127
@@ -499,7 +498,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t* __res
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
             if (lane == 0) {
-                mbar_arrive(&sm.h_ready[su]);
+                mbar_arrive(&sm.h_ready[sh]);
                 mbar_arrive(&sm.w_empty[sw]);
             }
             if (++sw == kTc2NW) {
