@@ -42,7 +42,10 @@ constexpr int kMidACols = kMidUnitK * 32;            // TMEM columns of one fp16
 constexpr int kMidNWMax = 4, kMidNXMax = 4, kMidNHMax = 4;
 
 __host__ __device__ constexpr int mid_nw(int bn) { return bn == 64 ? 3 : 4; }
-__host__ __device__ constexpr int mid_nx(int bn) { return bn == 32 ? 4 : 3; }
+__host__ __device__ constexpr int mid_nx(int bn) { return bn == 32 ? 4 : (bn == 256 ? 2 : 3); }
+// accumulator buffers: two (the epilogue of a strip overlaps the next strip's MMAs) while they fit beside
+// the fp16 weight buffers; one for 256-token tiles
+__host__ __device__ constexpr int mid_acc_bufs(int bn) { return bn <= 128 ? 2 : 1; }
 __host__ __device__ constexpr int mid_nh(int bn) { return bn == 32 ? 3 : (bn == 64 ? 2 : 4); }
 
 __host__ __device__ constexpr int mid_smem_bytes(int bn)
@@ -53,7 +56,7 @@ __host__ __device__ constexpr int mid_smem_bytes(int bn)
 // tensor-memory columns: two accumulators of BN columns, then the fp16 weight buffers
 __host__ __device__ constexpr uint32_t mid_tmem_cols(int bn)
 {
-    return 2 * bn + mid_nh(bn) * kMidACols <= 256 ? 256u : 512u;
+    return mid_acc_bufs(bn) * bn + mid_nh(bn) * kMidACols <= 256 ? 256u : 512u;
 }
 
 struct MidSmem {
@@ -111,7 +114,8 @@ gemm_mid_kernel(const __grid_constant__ CUtensorMap tmap_x, GemmArgs a)
     uint8_t* x_ring = base;                                   // 1024-byte aligned tiles (swizzled)
     uint8_t* w_ring = x_ring + kMidNX * kXStage;
     constexpr uint32_t kTmemCols = mid_tmem_cols(BN);
-    constexpr uint32_t kAColBase = 2 * BN;                    // first column of the fp16 weight buffers
+    constexpr int kAccBufs = mid_acc_bufs(BN);
+    constexpr uint32_t kAColBase = kAccBufs * BN;             // first column of the fp16 weight buffers
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int KT = a.K / kTile;
     const int KP = (KT + kMidUnitK - 1) / kMidUnitK;          // units per strip
@@ -221,8 +225,8 @@ gemm_mid_kernel(const __grid_constant__ CUtensorMap tmap_x, GemmArgs a)
             const bool odd_tail = (KT & 1) != 0;  // the last unit of a strip then holds one k-block
             for (int u = u0; u < u1 && ok;) {
                 const int u_end = min(u1, strip_end);
-                const int buf = seg & 1;
-                if (seg >= 2 && !tc_wait(&sm.acc_empty[buf], ((seg >> 1) - 1) & 1, &sm.abort)) break;
+                const int buf = seg % kAccBufs;
+                if (seg >= kAccBufs && !tc_wait(&sm.acc_empty[buf], (uint32_t)((seg / kAccBufs - 1) & 1), &sm.abort)) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t d_tmem = tmem + (uint32_t)(buf * BN);
                 for (int uu = u; uu < u_end; ++uu) {
@@ -345,11 +349,11 @@ gemm_mid_kernel(const __grid_constant__ CUtensorMap tmap_x, GemmArgs a)
         for (int u = u0; u < u1; ++seg) {
             const int strip = u / KP;
             const int u_end = min(u1, (strip + 1) * KP);
-            const int buf = seg & 1;
+            const int buf = seg % kAccBufs;
             // one lane polls (a segment lasts tens of microseconds: 128 spinning lanes would take issue
             // slots and shared-memory bandwidth from the threads that feed the tensor core)
             int got = 1;
-            if (lane == 0) got = tc_wait(&sm.acc_full[buf], (seg >> 1) & 1, &sm.abort) ? 1 : 0;
+            if (lane == 0) got = tc_wait(&sm.acc_full[buf], (uint32_t)((seg / kAccBufs) & 1), &sm.abort) ? 1 : 0;
             got = __shfl_sync(0xffffffffu, got, 0);
             if (!got) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -417,7 +421,17 @@ int launch_gemm_mid(const GemmArgs& a, cudaStream_t stream)
               kMidMaxM);
     EncodeTiledFn encode = encode_tiled_fn();
     EET_CHECK(encode != nullptr, "stream-K tensor-core GEMM: cuTensorMapEncodeTiled is not available from the driver");
-    const int bn = a.M <= 32 ? 32 : (a.M <= 64 || a.M % 128 != 0 ? 64 : 128);
+    static int force_bn = -1;
+    if (force_bn < 0) {
+        const char* e = getenv("EET_MID_BN");
+        force_bn = e ? atoi(e) : 0;
+    }
+    // token tile: the smallest that holds M; above 128 tokens 256-token tiles (half the activation traffic
+    // per flop, MMAs long enough to hide their issue cost) when every CTA still gets a decent run of units
+    const long long units = (long long)(a.N / 128) * ((a.K / kTile + kMidUnitK - 1) / kMidUnitK) * (a.B2 ? 2 : 1);
+    int bn = a.M <= 32 ? 32 : (a.M <= 64 ? 64 : 128);
+    if (a.M > 128 && units >= 16LL * sm_count()) bn = 256;
+    if (force_bn) bn = force_bn;
     CUtensorMap map;
     const cuuint64_t dims[2] = {(cuuint64_t)a.K, (cuuint64_t)a.M};
     const cuuint64_t strides[1] = {(cuuint64_t)a.K * sizeof(__half)};
@@ -429,7 +443,8 @@ int launch_gemm_mid(const GemmArgs& a, cudaStream_t stream)
     EET_CHECK(rc == CUDA_SUCCESS, "stream-K tensor-core GEMM: cuTensorMapEncodeTiled failed with code %d", (int)rc);
     if (bn == 32) return launch_mid<32>(map, a, stream);
     if (bn == 64) return launch_mid<64>(map, a, stream);
-    return launch_mid<128>(map, a, stream);
+    if (bn == 128) return launch_mid<128>(map, a, stream);
+    return launch_mid<256>(map, a, stream);
 }
 
 }  // namespace eet

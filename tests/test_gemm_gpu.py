@@ -207,18 +207,21 @@ def test_stream_k_accumulate_two_weights_exact_sums(M):
     assert _lib.device_status() == 0
 
 
-@pytest.mark.parametrize("KNM", [(512, 384, 600), (1024, 640, 1000), (256, 4096, 2048), (4096, 4096, 1024)])
+@pytest.mark.parametrize("KNM", [(512, 384, 600), (1024, 640, 1000), (256, 4096, 2048), (4096, 4096, 1024),
+                                 (4096, 11008, 300), (4096, 11008, 512)])
 def test_large_m_tensor_core_kernels(KNM):
     """M > 512: the 256 x 256 tile kernel when N is a multiple of 256 and there are enough tiles, else the
-    128-channel x 256-token kernel; ragged last token tile, residual epilogue."""
+    128-channel x 256-token kernel; ragged last token tile, residual epilogue.  The two 4096 x 11008 cases are
+    large enough for the stream-K kernel to choose its 256-token tiles (single accumulator buffer)."""
     K, N, M = KNM
     x, q, s = _case(K, N, M, seed=K + N + M)
     y = _run(x, q, s)
-    rows = torch.tensor([0, 1, 127, 128, 255, 256, 511, 512, M - 2, M - 1])
+    rows = torch.tensor([r for r in (0, 1, 127, 128, 255, 256, 511, 512, M - 2, M - 1) if r < M])
     ref = ops.gemm_w8a16_fp32(x[rows], q, s)
     assert ((y[rows].double() - ref).abs() <= 1e-2 * ref.abs().amax(1, keepdim=True)).all()
     exact = ops.gemm_w8a16(x[rows], q, s, exact=True).double()
     assert ((y[rows].double() - exact).abs() <= 2e-3 * ref.abs().amax(1, keepdim=True) + 1e-3).all()
     res = torch.randn(M, N, generator=torch.Generator().manual_seed(2)).half()
     yr = _run(x, q, s, residual=res)
-    assert torch.equal(yr[rows], ops.add_residual(y[rows], res[rows]))
+    # (M <= 512 sums with atomics: two runs may differ in the last fp16 bit)
+    assert torch.allclose(yr[rows].float(), ops.add_residual(y[rows], res[rows]).float(), rtol=2e-3, atol=2e-3)
