@@ -40,7 +40,7 @@ int noalloc_scratch(float** out)
 int gemm_w8a16_noalloc(const __half* A, const uint8_t* B, const __half* scale, __half* C, int M, int N, int K,
                        const __half* residual, cudaStream_t stream)
 {
-    EET_CHECK(M <= 16, "eet_gemm_w8a16_noalloc: M=%d exceeds 16 (larger M needs no scratch: use eet_gemm_w8a16)", M);
+    EET_CHECK(M <= 16, "eet_gemm_w8a16_noalloc: M=%d exceeds 16 (use eet_gemm_w8a16 with a caller-provided scratch)", M);
     EET_CHECK((size_t)M * (size_t)N <= kNoAllocMaxSums,
               "eet_gemm_w8a16_noalloc: M*N = %zu exceeds the built-in scratch of %zu sums", (size_t)M * (size_t)N,
               kNoAllocMaxSums);

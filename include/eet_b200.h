@@ -73,9 +73,10 @@ int eet_repack_ref_w8(const void* ref_packed, int K, int N, void* packed, void* 
  * W8A16 GEMM
  * ---------------------------------------------------------------------------------------------- */
 
-/* Scratch needed by eet_gemm_w8a16 for a problem of this size (fp32 sums of up to 128 rows).  The scratch
- * must be zero before its first use (e.g. cudaMemset once after allocation); every call leaves it zero
- * again.  Calls that share one scratch buffer must not overlap on the GPU. */
+/* Scratch needed by eet_gemm_w8a16 for a problem of this size: M * N fp32 sums up to M = 512 (the stream-K
+ * kernels add partial sums there), 128 rows above that (only used when the shape has no large-tile kernel).
+ * The scratch must be zero before its first use (e.g. cudaMemset once after allocation); every call leaves
+ * it zero again.  Calls that share one scratch buffer must not overlap on the GPU. */
 size_t eet_gemm_w8a16_workspace_bytes(int M, int N, int K);
 
 /*
@@ -89,13 +90,16 @@ size_t eet_gemm_w8a16_workspace_bytes(int M, int N, int K);
  *             projection GEMMs in the reference (csrc/core/add_bias.cu:22-28) fused in.
  *   residual  device fp16 [M][N] for epilogue 1, else NULL (may alias C)
  * M may be any value >= 0; K and N must be multiples of 64; pointers 16-byte aligned.
+ * Kernels: M <= 16 TMA-staged skinny kernel; 16 < M <= 512 (N % 128 == 0) stream-K tcgen05 kernel; above
+ * that tcgen05 kernels with 256 x 256 or 128 x 256 output tiles that need no scratch; shapes none of them
+ * takes fall back to the skinny kernel in groups of 128 rows.
  */
 int eet_gemm_w8a16(const void* A, const void* packedB, const void* scale, void* C, int M, int N, int K,
                    const void* residual, int epilogue, void* ws, size_t ws_bytes, void* stream);
 
 /*
- * The two halves of eet_gemm_w8a16 for small M (the decode regime), exposed so that the second half can be
- * fused into the kernel that consumes the product.
+ * The two halves of eet_gemm_w8a16 for M <= 512 (the decode regime and small prefills), exposed so that the
+ * second half can be fused into the kernel that consumes the product.
  *
  * eet_gemm_w8a16_accum ADDS sum_k A[m][k] * q[k][n] (q = the int8 weight values, unscaled) into the fp32
  * buffer sums[M][N]; with packedB2 / sums2 a second weight of the same shape (the FFN "up" projection next
@@ -118,7 +122,7 @@ int eet_gemm_w8a16_finalize(float* sums, const void* scale, const void* residual
  * device-wide stall of cudaMalloc - and therefore cannot hand eet_gemm_w8a16 its zeroed fp32 scratch.
  * The scratch is a fixed 2 MiB array inside the library's device image (held by every GPU that loads the
  * library, until the process ends): M * N may not exceed 16 * 32768, M may not exceed 16; larger problems
- * are refused with an error (for M > 16 eet_gemm_w8a16 needs no scratch anyway).  The call allocates
+ * are refused with an error.  The call allocates
  * nothing.  Its first use on a device looks up the array's device address, so make that first call outside
  * any stream capture.  All calls on a device share the array: it is cleared at the start of each call, and
  * two calls that overlap on the GPU (different streams) race.
