@@ -420,38 +420,46 @@ __global__ void qkv_split_store_kernel(const __half* __restrict__ qkv, __half* _
                                        __half* __restrict__ kcache, __half* __restrict__ vcache, int S, int H, int D,
                                        int T_max, int rope, float rope_base)
 {
-    const int s = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
-    const int i = threadIdx.x;
+    // a thread owns 8 consecutive dims of the first half of a head and their partners in the second half
+    // (the NeoX pairing is (i, i + D/2)): 16-byte loads and stores; blockDim / (D/16) heads per CTA
     const int half_d = D >> 1;
-    if (i >= half_d) return;
+    const int tph = half_d >> 3;                       // threads per head
+    const int s = blockIdx.x, b = blockIdx.z;
+    const int h = blockIdx.y * (blockDim.x / tph) + threadIdx.x / tph;
+    if (h >= H) return;
+    const int i0 = (threadIdx.x % tph) * 8;
     const size_t inner = (size_t)H * D;
     const __half* src = qkv + ((size_t)b * S + s) * 3 * inner + (size_t)h * D;
-    float q1 = __half2float(src[i]), q2 = __half2float(src[i + half_d]);
-    float k1 = __half2float(src[inner + i]), k2 = __half2float(src[inner + i + half_d]);
-    const __half v1 = src[2 * inner + i], v2 = src[2 * inner + i + half_d];
-    __half oq1, oq2, ok1, ok2;
+    uint4 q1 = *reinterpret_cast<const uint4*>(src + i0), q2 = *reinterpret_cast<const uint4*>(src + i0 + half_d);
+    uint4 k1 = *reinterpret_cast<const uint4*>(src + inner + i0);
+    uint4 k2 = *reinterpret_cast<const uint4*>(src + inner + i0 + half_d);
+    const uint4 v1 = *reinterpret_cast<const uint4*>(src + 2 * inner + i0);
+    const uint4 v2 = *reinterpret_cast<const uint4*>(src + 2 * inner + i0 + half_d);
     if (rope) {
-        const float ang = (float)s / powf(rope_base, (float)(2 * i) / (float)D);
-        const float c = cosf(ang), sn = sinf(ang);
-        oq1 = __float2half(q1 * c - q2 * sn);
-        oq2 = __float2half(q2 * c + q1 * sn);
-        ok1 = __float2half(k1 * c - k2 * sn);
-        ok2 = __float2half(k2 * c + k1 * sn);
-    }
-    else {
-        oq1 = src[i];
-        oq2 = src[i + half_d];
-        ok1 = src[inner + i];
-        ok2 = src[inner + i + half_d];
+        __half* q1h = reinterpret_cast<__half*>(&q1);
+        __half* q2h = reinterpret_cast<__half*>(&q2);
+        __half* k1h = reinterpret_cast<__half*>(&k1);
+        __half* k2h = reinterpret_cast<__half*>(&k2);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const float ang = (float)s / powf(rope_base, (float)(2 * (i0 + e)) / (float)D);
+            const float c = cosf(ang), sn = sinf(ang);
+            const float a1 = __half2float(q1h[e]), a2 = __half2float(q2h[e]);
+            const float b1 = __half2float(k1h[e]), b2 = __half2float(k2h[e]);
+            q1h[e] = __float2half(a1 * c - a2 * sn);
+            q2h[e] = __float2half(a2 * c + a1 * sn);
+            k1h[e] = __float2half(b1 * c - b2 * sn);
+            k2h[e] = __float2half(b2 * c + b1 * sn);
+        }
     }
     __half* qd = q_out + (((size_t)b * H + h) * S + s) * D;
-    qd[i] = oq1;
-    qd[i + half_d] = oq2;
+    *reinterpret_cast<uint4*>(qd + i0) = q1;
+    *reinterpret_cast<uint4*>(qd + i0 + half_d) = q2;
     const size_t c_off = (((size_t)b * H + h) * T_max + s) * D;
-    kcache[c_off + i] = ok1;
-    kcache[c_off + i + half_d] = ok2;
-    vcache[c_off + i] = v1;
-    vcache[c_off + i + half_d] = v2;
+    *reinterpret_cast<uint4*>(kcache + c_off + i0) = k1;
+    *reinterpret_cast<uint4*>(kcache + c_off + i0 + half_d) = k2;
+    *reinterpret_cast<uint4*>(vcache + c_off + i0) = v1;
+    *reinterpret_cast<uint4*>(vcache + c_off + i0 + half_d) = v2;
 }
 
 // Beam-search cache reordering: cache[b] <- cache[index[b]] for the first `step` positions
@@ -607,13 +615,17 @@ int launch_add_residual(__half* out, const __half* in, size_t count, cudaStream_
 int launch_qkv_split_store(const __half* qkv, __half* q_out, __half* kcache, __half* vcache, int B, int S, int H,
                            int D, int T_max, int rope, float rope_base, cudaStream_t stream)
 {
-    EET_CHECK(D % 2 == 0 && D <= 2048, "qkv_split_store: head size %d unsupported", D);
+    EET_CHECK(D % 16 == 0 && D <= 2048, "qkv_split_store: head size %d unsupported (multiples of 16 up to 2048)", D);
     EET_CHECK(S <= T_max, "qkv_split_store: prompt length %d exceeds the cache length %d", S, T_max);
-    EET_CHECK(H <= 65535 && B <= 65535, "qkv_split_store: head count / batch too large for the grid");
+    EET_CHECK(B <= 65535, "qkv_split_store: batch too large for the grid");
     if (B == 0 || S == 0) return 0;
-    const int threads = (D / 2 + 31) / 32 * 32;
-    qkv_split_store_kernel<<<dim3(S, H, B), threads, 0, stream>>>(qkv, q_out, kcache, vcache, S, H, D, T_max, rope,
-                                                                 rope_base);
+    const int tph = D / 16;                         // threads per head
+    int heads_per_cta = 256 / tph;
+    if (heads_per_cta < 1) heads_per_cta = 1;
+    if (heads_per_cta > H) heads_per_cta = H;
+    const int threads = heads_per_cta * tph;
+    qkv_split_store_kernel<<<dim3(S, (H + heads_per_cta - 1) / heads_per_cta, B), threads, 0, stream>>>(
+        qkv, q_out, kcache, vcache, S, H, D, T_max, rope, rope_base);
     EET_LAUNCH_CHECK();
     return 0;
 }

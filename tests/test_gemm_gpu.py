@@ -208,11 +208,13 @@ def test_stream_k_accumulate_two_weights_exact_sums(M):
 
 
 @pytest.mark.parametrize("KNM", [(512, 384, 600), (1024, 640, 1000), (256, 4096, 2048), (4096, 4096, 1024),
-                                 (4096, 11008, 300), (4096, 11008, 512)])
+                                 (4096, 11008, 300), (4096, 11008, 512), (128, 14208, 512)])
 def test_large_m_tensor_core_kernels(KNM):
     """M > 512: the 256 x 256 tile kernel when N is a multiple of 256 and there are enough tiles, else the
     128-channel x 256-token kernel; ragged last token tile, residual epilogue.  The two 4096 x 11008 cases are
-    large enough for the stream-K kernel to choose its 256-token tiles (single accumulator buffer)."""
+    large enough for the stream-K kernel to choose its 256-token tiles (single accumulator buffer); 128 x 14208
+    gives every CTA of that kernel three one-unit strips, i.e. a third accumulation that has to wait for the
+    epilogue of the first."""
     K, N, M = KNM
     x, q, s = _case(K, N, M, seed=K + N + M)
     y = _run(x, q, s)
