@@ -137,8 +137,39 @@ def test_prefill(S, mode):
                               None if alibi_c is None else alibi_c.data_ptr(), S, _stream()))
     torch.cuda.synchronize()
     got = ctx.cpu().view(B, S, H, D).transpose(1, 2)
-    # the oracle rounds probabilities to fp16 like the reference's score buffer; this kernel keeps fp32
+    # oracle and kernel both feed fp16 probabilities to P.V, but normalise at different points (the oracle
+    # rounds p / sum, the blockwise kernel rounds exp(s - running max) and divides at the end)
     assert torch.allclose(got.float(), ref.float(), atol=4e-3, rtol=4e-3)
+
+
+@pytest.mark.parametrize("case", [(200, [70, 130], "pad"), (512, [0, 0], "plain"), (300, [0, 0], "alibi")])
+def test_prefill_long_prompts(case):
+    """Prompts of several 64-query tiles: left padding that swallows whole key blocks and whole query tiles
+    (their rows must come out zero), the configs[2] prompt length, and ALiBi across tiles."""
+    from eet_b200._lib import check, lib
+    S, pads, mode = case
+    B, H, D, T = 2, 2, 128, 520
+    gen = torch.Generator().manual_seed(S)
+    q, k, v = (torch.randn(B, H, S, D, generator=gen).half() for _ in range(3))
+    pad = torch.tensor(pads, dtype=torch.long) if mode == "pad" else None
+    alibi = ops.alibi_mask(H, T).half()[:, :S, :S].contiguous() if mode == "alibi" else None
+    ref = ops.prefill_attention(q, k, v, pad, alibi)
+    kc = torch.zeros(B, H, T, D, dtype=torch.float16, device="cuda")
+    vc = torch.zeros_like(kc)
+    kc[:, :, :S], vc[:, :, :S] = k.cuda(), v.cuda()
+    ctx = torch.full((B, S, H * D), 7.0, dtype=torch.float16, device="cuda")
+    qc = q.cuda()
+    pad_c = None if pad is None else pad.cuda()
+    alibi_c = None if alibi is None else alibi.cuda()
+    check(lib.eet_prefill_mha(qc.data_ptr(), kc.data_ptr(), vc.data_ptr(), ctx.data_ptr(), B, S, H, D, T,
+                              None if pad_c is None else pad_c.data_ptr(),
+                              None if alibi_c is None else alibi_c.data_ptr(), S, _stream()))
+    torch.cuda.synchronize()
+    got = ctx.cpu().view(B, S, H, D).transpose(1, 2)
+    assert torch.allclose(got.float(), ref.float(), atol=4e-3, rtol=4e-3)
+    if mode == "pad":
+        for b, p_len in enumerate(pads):
+            assert float(got[b, :, :p_len].abs().max()) == 0.0   # rows inside the padding are zeroed
 
 
 def test_decode_finishes_projection_sums_itself():

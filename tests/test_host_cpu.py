@@ -85,3 +85,19 @@ def test_convert_weights_data_types():
     assert d["layer.0.ffn.output.weight"].shape == (16, 8) and d["layer.0.ffn.output.weight"].dtype == torch.float16
     assert d["layer.0.self_attn.qkv_proj.weight"].shape == (8, 24)
     assert not any(k.endswith(".scale") for k in d)
+
+
+def test_fp16_weight_shards_are_plain_slices():
+    """Tensor-parallel shards of the fp16 twin's weights: columns [lo, hi) of each of the Q | K | V blocks
+    (column-parallel) and rows [lo, hi) (row-parallel); no scales."""
+    import types
+    from eet_b200 import modeling
+    fake_tp = types.SimpleNamespace(size=2, rank=1)
+    w = torch.arange(4 * 12, dtype=torch.float16).view(4, 12)          # K = 4, N = 3 blocks of 4
+    cols, s = modeling._shard_cols(w, modeling._EMPTY, fake_tp, 2, 4, 3)
+    assert s.numel() == 0 and cols.shape == (4, 6)
+    assert torch.equal(cols, torch.cat([w[:, 2:4], w[:, 6:8], w[:, 10:12]], 1))
+    rows, s = modeling._shard_rows(w, modeling._EMPTY, fake_tp, 1, 3)
+    assert torch.equal(rows, w[1:3]) and rows.is_contiguous()
+    same, _ = modeling._shard_cols(w, modeling._EMPTY, None, 0, 4, 3)
+    assert same is w
