@@ -286,8 +286,8 @@ def cpu_decode_sample(steps, layers=1, threads=None):
         dec.forward(x, False)
     dt = (time.perf_counter() - t0) / steps
     tok_s = BATCH / (dt * cfg.num_hidden_layers / layers)
-    sample = (f"{steps} decode steps of {layers} of 32 layers (batch {BATCH}, history {PROMPT}), time scaled by "
-              f"32/{layers}; torch fp32 ops on {threads} threads")
+    sample = (f"{steps} decode steps of {layers} of {cfg.num_hidden_layers} layers (batch {BATCH}, history {PROMPT}), "
+              f"time scaled by {cfg.num_hidden_layers}/{layers}; torch fp32 ops on {threads} threads")
     return tok_s, threads, sample, dt
 
 
@@ -300,10 +300,10 @@ def run_reference(args):
     steps = max(1, min(args.steps, 16))
     tok_s, threads, sample, dt = cpu_decode_sample(steps)
     line = {"impl": "reference", "metric": METRIC, "value": round(tok_s, 3), "unit": UNIT, "n_gpus": args.gpus,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(dt * 32 * 1e3, 3),
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(dt * CFG["num_hidden_layers"] * 1e3, 3),
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32 (cpu port of f16 path)",
             "data": "synthetic",
-            "config": {"workload": "llama7b_arch_int8_decode_b8_prompt512", "global_batch": BATCH, "seq_len": PROMPT},
+            "config": {"workload": WORKLOAD, "global_batch": BATCH, "seq_len": PROMPT},
             "cpu_baseline": {"value": round(tok_s, 3), "unit": UNIT, "cores": threads, "kind": "port",
                              "sample": sample},
             "e2e": {"value": round(tok_s, 3), "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
