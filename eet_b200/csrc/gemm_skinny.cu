@@ -12,8 +12,9 @@
 //    of the weight array, whatever N and K are.
 //  * A producer warp feeds a ring of shared-memory stages with 1-D bulk copies (TMA engine,
 //    cp.async.bulk + mbarrier complete_tx, L2 evict-first hint): 32 KiB of weights (eight tiles) per stage,
-//    two stages per CTA, two CTAs per SM (measured best among 16-40 KiB stages x 2-5 stages).  The matching slice of the activations (a few KiB, L2
-//    resident) is staged beside it by the consumer warps with plain 16-byte loads, one stage ahead.
+//    two stages per CTA, two CTAs per SM (measured best among 16-40 KiB stages x 2-5 stages and 2-3 CTAs
+//    per SM).  The matching slice of the activations (a few KiB, L2 resident) is staged beside it by the
+//    consumer warps with plain 16-byte loads, one stage ahead.
 //  * Eight consumer warps share a stage by channel group and tile half: 16-byte shared loads deliver
 //    exactly the A fragments of mma.m16n8k16 (16 channels x 64 reduction indices per pair of loads),
 //    bytes become fp16 in registers (prmt + sub.f16x2) and feed the tensor cores with up to 8 tokens as

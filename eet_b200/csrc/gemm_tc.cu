@@ -1,5 +1,5 @@
-// W8A16 tensor-core GEMM for the prefill regime (M > 16): C[M,N] = A[M,K] (fp16) x dequant(B), B in the
-// W8T64 layout, per-channel fp16 scale (and optional fp16 residual) in the epilogue.
+// W8A16 tensor-core GEMM for the prefill regime (M > 512; smaller M go to the stream-K kernel):
+// C[M,N] = A[M,K] (fp16) x dequant(B), B in the W8T64 layout, per-channel fp16 scale (and optional fp16 residual) in the epilogue.
 //
 // Replaces the reference's fpA_intB GEMM (kernel cutlass_extensions/.../gemm/kernel/fpA_intB_gemm.h:60-486,
 // mainloop .../threadblock/dq_mma_multistage.h:490-583: mma.sync m16n8k16 with int8 -> fp16 conversion in
@@ -17,7 +17,8 @@
 //  * warp 1 (one lane) issues four tcgen05.mma (M128 x BN x K16, fp16 in, fp32 accumulate in TMEM) per
 //    k-block and commits them to the stage's "empty" mbarrier, which releases the stage to the producer.
 //  * after the last k-block warps 2-5 read the accumulator with tcgen05.ld (lane = channel), multiply by
-//    the channel's scale, round once to fp16, add the residual if asked and store.
+//    the channel's scale, round once to fp16, and pass 128 x 32 blocks through shared memory so that the
+//    stores (and the residual loads) are 16-byte accesses of whole 256-byte row segments.
 //  Three-stage ring of {8 KiB int8 weights, 16 KiB fp16 weights, BN x 128 B activations}.
 //  Every wait is bounded; a wait that runs out sets the device status word, and the CTA still frees its
 //  tensor memory before it returns.
@@ -585,8 +586,9 @@ int launch_tc(const CUtensorMap& map, const uint8_t* B, const __half* scale, __h
 
 }  // namespace
 
-// Below this many tokens the skinny kernel (weights streamed once per 16-token chunk row, the chunk rows of
-// one launch sharing them through L2) is faster than a tensor-core tile that leaves most SMs idle.
+// Smallest M these kernels accept.  The dispatcher sends M <= 512 to the stream-K kernel first; only shapes
+// that kernel does not take can arrive here with fewer tokens, and below 65 a one-tile-per-CTA kernel would
+// leave most SMs idle, so the skinny kernel serves those.
 constexpr int kTcMinM = 65;
 
 bool gemm_tc_supported(int M, int N, int K)
