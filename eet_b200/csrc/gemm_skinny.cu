@@ -101,36 +101,45 @@ gemm_skinny_kernel(GemmArgs a)
     constexpr int kStages = stage_count(NB);
     constexpr int kStageBytes = stage_bytes(NB);
 
-    if (threadIdx.x == 0) {
+    // The producer lane sets the barriers up itself and requests the first stages BEFORE the block-wide
+    // barrier: nobody else touches the ring until then, and on a 5-10 us kernel the few hundred nanoseconds
+    // that the other warps need to arrive are worth having the first 64 KiB in flight.
+    // Weights are constant inputs: no need to wait for the preceding kernel either.
+    const bool is_producer = (warp == kConsumerWarps) && (lane == 0);
+    int p_it = 0, p_g = g0;
+    auto issue_stage = [&]() {
+        const int nt = p_g / KT, kb = p_g - nt * KT;
+        const int nb_tiles = min(min(kStageTiles, KT - kb), g1 - p_g);
+        const int s = p_it % kStages;
+        mbar_arrive_expect_tx(&sm.full[s], (uint32_t)(nb_tiles * kTileBytes));
+        const uint8_t* src = (p_g < G1) ? a.B + (size_t)p_g * kTileBytes : a.B2 + (size_t)(p_g - G1) * kTileBytes;
+        bulk_g2s_stream(dyn_smem + (size_t)s * kStageBytes, src, (uint32_t)(nb_tiles * kTileBytes), &sm.full[s]);
+        p_g += nb_tiles;
+        ++p_it;
+    };
+    if (is_producer) {
         for (int s = 0; s < kStages; ++s) {
             mbar_init(&sm.full[s], 1);
             mbar_init(&sm.empty[s], kConsumerWarps);
         }
         sm.abort = 0;
         mbar_fence_init();
+        while (p_it < kStages && p_g < g1) issue_stage();
     }
     __syncthreads();
 
     if (warp == kConsumerWarps) {
         // ------------------------------------------------------------------ producer warp (one lane)
-        // Weights are constant inputs: no need to wait for the preceding kernel.
         if (lane == 0) {
-            int it = 0;
-            for (int g = g0; g < g1; ++it) {
-                const int nt = g / KT, kb = g - nt * KT;
-                const int nb_tiles = min(min(kStageTiles, KT - kb), g1 - g);
-                const int s = it % kStages;
-                if (it >= kStages && !sm.abort) {
-                    if (!mbar_wait_bounded(&sm.empty[s], ((it / kStages) - 1) & 1)) {
+            while (p_g < g1) {
+                const int s = p_it % kStages;
+                if (!sm.abort) {
+                    if (!mbar_wait_bounded(&sm.empty[s], ((p_it / kStages) - 1) & 1)) {
                         sm.abort = 1;
                         g_device_status = 1;
                     }
                 }
-                mbar_arrive_expect_tx(&sm.full[s], (uint32_t)(nb_tiles * kTileBytes));
-                const uint8_t* src = (g < G1) ? a.B + (size_t)g * kTileBytes : a.B2 + (size_t)(g - G1) * kTileBytes;
-                bulk_g2s_stream(dyn_smem + (size_t)s * kStageBytes, src, (uint32_t)(nb_tiles * kTileBytes),
-                                &sm.full[s]);
-                g += nb_tiles;
+                issue_stage();
             }
         }
         return;
