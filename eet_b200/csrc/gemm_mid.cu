@@ -147,6 +147,36 @@ gemm_mid_kernel(const __grid_constant__ CUtensorMap tmap_x, GemmArgs a)
         sm.abort = 0;
         mbar_fence_init();
     }
+    // ------------------------------------------------------------------ weight producer (thread 0)
+    // Constant inputs: requested without waiting for the preceding kernel - and the first ring of requests
+    // goes out before the block-wide barrier and the tensor-memory allocation, which nobody needs for it.
+    int w_s = 0, w_fill = 0, w_u = u0;
+    uint32_t w_ph = 1;   // parity of the previous round of slot w_s
+    int w_strip = u0 / KP, w_kp = u0 - (u0 / KP) * KP;
+    auto issue_w = [&]() {
+        const int kb = w_kp * kMidUnitK;
+        const uint32_t bytes = (uint32_t)min(kMidUnitK, KT - kb) * kTileBytes;   // per channel half
+        const uint8_t* Bm = (w_strip < strips1) ? a.B : a.B2;
+        const int st = (w_strip < strips1) ? w_strip : w_strip - strips1;
+        const uint8_t* w0 = Bm + ((size_t)(2 * st) * KT + kb) * kTileBytes;
+        uint8_t* dst = w_ring + (size_t)w_s * kMidWStage;
+        mbar_arrive_expect_tx(&sm.w_full[w_s], 2 * bytes);
+        bulk_g2s_stream(dst, w0, bytes, &sm.w_full[w_s]);
+        bulk_g2s_stream(dst + kMidWStage / 2, w0 + (size_t)KT * kTileBytes, bytes, &sm.w_full[w_s]);
+        ++w_fill;
+        ++w_u;
+        if (++w_s == kMidNW) {
+            w_s = 0;
+            w_ph ^= 1;
+        }
+        if (++w_kp == KP) {
+            w_kp = 0;
+            ++w_strip;
+        }
+    };
+    if (threadIdx.x == 0) {
+        while (w_fill < kMidNW && w_u < u1) issue_w();
+    }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)),
                      "r"(kTmemCols)
@@ -159,32 +189,10 @@ gemm_mid_kernel(const __grid_constant__ CUtensorMap tmap_x, GemmArgs a)
     const uint32_t tmem = sm.tmem_base;
 
     if (warp == 0) {
-        // ------------------------------------------------------------------ weight producer
-        // (constant inputs: requested without waiting for the preceding kernel)
         if (lane == 0) {
-            int s = 0, fill = 0;
-            uint32_t ph = 1;   // parity of the previous round of slot s
-            int strip = u0 / KP, kp = u0 - strip * KP;
-            for (int u = u0; u < u1; ++u) {
-                if (fill >= kMidNW && !tc_wait(&sm.w_empty[s], ph, &sm.abort)) break;
-                const int kb = kp * kMidUnitK;
-                const uint32_t bytes = (uint32_t)min(kMidUnitK, KT - kb) * kTileBytes;   // per channel half
-                const uint8_t* Bm = (strip < strips1) ? a.B : a.B2;
-                const int st = (strip < strips1) ? strip : strip - strips1;
-                const uint8_t* w0 = Bm + ((size_t)(2 * st) * KT + kb) * kTileBytes;
-                uint8_t* dst = w_ring + (size_t)s * kMidWStage;
-                mbar_arrive_expect_tx(&sm.w_full[s], 2 * bytes);
-                bulk_g2s_stream(dst, w0, bytes, &sm.w_full[s]);
-                bulk_g2s_stream(dst + kMidWStage / 2, w0 + (size_t)KT * kTileBytes, bytes, &sm.w_full[s]);
-                ++fill;
-                if (++s == kMidNW) {
-                    s = 0;
-                    ph ^= 1;
-                }
-                if (++kp == KP) {
-                    kp = 0;
-                    ++strip;
-                }
+            while (w_u < u1) {
+                if (!tc_wait(&sm.w_empty[w_s], w_ph, &sm.abort)) break;
+                issue_w();
             }
         }
     }
