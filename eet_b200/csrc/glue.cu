@@ -139,9 +139,22 @@ rmsnorm_finalize_kernel(float* __restrict__ sums, const __half* __restrict__ sca
     __shared__ float red[32];
     __shared__ float s_inv;
     pdl_launch_dependents();
-    pdl_wait();
     const int row = blockIdx.x;
     const int nv = n >> 3;
+    // the per-channel scales and the norm weights are constants: fetched while the preceding GEMM still runs,
+    // so that neither of the two phases below waits for them
+    uint4 scv[2], gv[2];
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+        const int i = threadIdx.x + j * blockDim.x;
+        scv[j] = make_uint4(0u, 0u, 0u, 0u);
+        gv[j] = scv[j];
+        if (i < nv) {
+            gv[j] = reinterpret_cast<const uint4*>(gamma)[i];
+            if (sums != nullptr) scv[j] = reinterpret_cast<const uint4*>(scale)[i];
+        }
+    }
+    pdl_wait();
     const uint4* rr = reinterpret_cast<const uint4*>(residual + (size_t)row * n);
     uint4 h[2];
     float ss = 0.f;
@@ -153,8 +166,7 @@ rmsnorm_finalize_kernel(float* __restrict__ sums, const __half* __restrict__ sca
             if (sums != nullptr) {
                 float v[8];
                 load_sums8(sums + (size_t)row * n + (size_t)i * 8, v);
-                const uint4 sc = reinterpret_cast<const uint4*>(scale)[i];
-                h[j] = finalize8(v, sc, &h[j]);
+                h[j] = finalize8(v, scv[j], &h[j]);
                 reinterpret_cast<uint4*>(h_out + (size_t)row * n)[i] = h[j];
             }
             const __half2* hh = reinterpret_cast<const __half2*>(&h[j]);
@@ -179,9 +191,8 @@ rmsnorm_finalize_kernel(float* __restrict__ sums, const __half* __restrict__ sca
     for (int j = 0; j < 2; ++j) {
         const int i = threadIdx.x + j * blockDim.x;
         if (i < nv) {
-            const uint4 g = reinterpret_cast<const uint4*>(gamma)[i];
             const __half2* hh = reinterpret_cast<const __half2*>(&h[j]);
-            const __half2* gh = reinterpret_cast<const __half2*>(&g);
+            const __half2* gh = reinterpret_cast<const __half2*>(&gv[j]);
             uint4 o;
             __half2* oh = reinterpret_cast<__half2*>(&o);
 #pragma unroll
@@ -234,10 +245,13 @@ rmsnorm_finalize_tp_kernel(TpPeers peers, float* __restrict__ local_sums, int* _
     __shared__ float s_part;     // this CTA's share of the row's sum of squares, read by the cluster
     __shared__ int s_epoch;
     pdl_launch_dependents();
-    pdl_wait();   // this rank's GEMM (and everything before it) is complete
     const int slices = (int)cluster.num_blocks();
     const int slice = (int)cluster.block_rank();
     const int row = blockIdx.x / slices;
+    // constants first, while the preceding GEMM still runs
+    const uint4 sc = reinterpret_cast<const uint4*>(scale)[slice * blockDim.x + threadIdx.x];
+    const uint4 g = reinterpret_cast<const uint4*>(gamma)[slice * blockDim.x + threadIdx.x];
+    pdl_wait();   // this rank's GEMM (and everything before it) is complete
     // every CTA of the row derives the epoch from the counter; the row's first CTA advances it afterwards
     if (threadIdx.x == 0) s_epoch = epochs[peers.which * kTpRows + row] + 1;
     __syncthreads();
@@ -303,7 +317,6 @@ rmsnorm_finalize_tp_kernel(TpPeers peers, float* __restrict__ local_sums, int* _
         }
     }
     uint4 h = reinterpret_cast<const uint4*>(residual + (size_t)row * n)[i];
-    const uint4 sc = reinterpret_cast<const uint4*>(scale)[i];
     h = finalize8(v, sc, &h);
     reinterpret_cast<uint4*>(h_out + (size_t)row * n)[i] = h;
     float ss = 0.f;
@@ -327,7 +340,6 @@ rmsnorm_finalize_tp_kernel(TpPeers peers, float* __restrict__ local_sums, int* _
     if (slice == 0 && threadIdx.x == 0) epochs[peers.which * kTpRows + row] = (int)epoch;
     const float inv = rsqrtf(total / n + eps);
     {
-        const uint4 g = reinterpret_cast<const uint4*>(gamma)[i];
         const __half2* gh = reinterpret_cast<const __half2*>(&g);
         uint4 o;
         __half2* oh = reinterpret_cast<__half2*>(&o);
@@ -374,15 +386,19 @@ swiglu_finalize_kernel(float* __restrict__ gate_sums, const __half* __restrict__
                        const __half* __restrict__ up_scale, __half* __restrict__ act, int n, size_t nvec)
 {
     pdl_launch_dependents();
-    pdl_wait();
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= nvec) return;
-    const int col = (int)((i * 8) % (size_t)n);
+    const bool live = i < nvec;
+    const int col = live ? (int)((i * 8) % (size_t)n) : 0;
+    // constants first, while the preceding GEMM still runs
+    const uint4 gsc = *reinterpret_cast<const uint4*>(gate_scale + col);
+    const uint4 usc = *reinterpret_cast<const uint4*>(up_scale + col);
+    pdl_wait();
+    if (!live) return;
     float gv[8], uv[8];
     load_sums8(gate_sums + i * 8, gv);
     load_sums8(up_sums + i * 8, uv);
-    const uint4 g = finalize8(gv, *reinterpret_cast<const uint4*>(gate_scale + col), nullptr);
-    const uint4 u = finalize8(uv, *reinterpret_cast<const uint4*>(up_scale + col), nullptr);
+    const uint4 g = finalize8(gv, gsc, nullptr);
+    const uint4 u = finalize8(uv, usc, nullptr);
     const __half2* gh = reinterpret_cast<const __half2*>(&g);
     const __half2* uh = reinterpret_cast<const __half2*>(&u);
     uint4 o;
