@@ -130,15 +130,18 @@ decode_mha_kernel(DecodeAttnArgs a)
         mbar_fence_init();
     }
 
+    pdl_launch_dependents();
+    __syncthreads();  // barriers initialised (before the wait below, so that nothing stands between it and the
+                      // producer's first request)
     // everything this kernel reads that an earlier kernel of the same step produced (the projection of the
     // new token, the device-resident step) comes after this wait
-    pdl_launch_dependents();
     pdl_wait();
     const int step = a.step_dev ? *a.step_dev : a.step;
     const size_t inner = (size_t)a.H * D;
 
-    // ---- slice of the history owned by this CTA ----
-    const int chunk = (((step + splits - 1) / splits) + kAttnTile - 1) / kAttnTile * kAttnTile;
+    // ---- slice of the history owned by this CTA: equal numbers of time steps (not of tiles: with 580 steps
+    // and two CTAs that is 290 + 290, ten tiles each, instead of 320 + 260) ----
+    const int chunk = (step + splits - 1) / splits;
     const int t_begin = split * chunk;
     const int t_end = min(step, t_begin + chunk);
     int pad = 0;
@@ -146,7 +149,6 @@ decode_mha_kernel(DecodeAttnArgs a)
     const int t_first = max(t_begin, pad / kAttnTile * kAttnTile);  // whole tiles left of the padding are skipped
     const int n_tiles = (t_end > t_first) ? (t_end - t_first + kAttnTile - 1) / kAttnTile : 0;
     const size_t cache_row0 = ((size_t)b * a.H + h) * a.T_max;
-    __syncthreads();  // barriers initialised
 
     if (warp == kAttnConsumerWarps) {
         // ------------------------------------------------------------------ producer warp (one lane)
