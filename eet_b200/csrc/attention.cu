@@ -93,8 +93,10 @@ struct AttnSmem {
     __half q[128], k[128], v[128];
     float m[kHalfWarps], l[kHalfWarps];
     float acc[kHalfWarps][128];
-    float c_acc[128];  // this CTA's merged partial, read by cluster rank 0 through distributed shared memory
-    float c_ml[2];
+    // the merged partial (max, sum, accumulator) of every CTA of the cluster, written into cluster rank 0's
+    // copy of this structure through distributed shared memory
+    float c_acc[8][128];
+    float c_ml[8][2];
     volatile int abort;
 };
 
@@ -343,39 +345,38 @@ decode_mha_kernel(DecodeAttnArgs a)
                 l += sm.l[w] * c;
                 acc += sm.acc[w][tid] * c;
             }
-            sm.c_acc[tid] = acc;
+            // push the partial into rank 0's shared memory: after the cluster barrier rank 0 merges from its
+            // own memory, and the other CTAs may leave at once
+            float* dst_acc = cluster.map_shared_rank(&sm.c_acc[0][0], 0);
+            dst_acc[split * 128 + tid] = acc;
             if (tid == 0) {
-                sm.c_ml[0] = m;
-                sm.c_ml[1] = l;
+                float* dst_ml = cluster.map_shared_rank(&sm.c_ml[0][0], 0);
+                dst_ml[split * 2 + 0] = m;
+                dst_ml[split * 2 + 1] = l;
             }
         }
     }
 
     // ---- merge the CTAs of the cluster; rank 0 writes the context ----
     cluster.sync();
-    if (split == 0 && a.qkv_sums != nullptr) {
+    if (split != 0) return;
+    if (a.qkv_sums != nullptr) {
         // every CTA of the cluster has read the projection sums of this (batch, head): put them back to zero
         for (int e = tid; e < 3 * D; e += kAttnThreads) {
             __stcg(a.qkv_sums + (size_t)b * 3 * inner + (size_t)(e / D) * inner + (size_t)h * D + (e % D), 0.f);
         }
     }
-    if (split == 0 && tid < D) {
+    if (tid < D) {
         float m = -1e20f;
-        for (int r = 0; r < splits; ++r) {
-            const float* rml = cluster.map_shared_rank(sm.c_ml, r);
-            m = fmaxf(m, rml[0]);
-        }
+        for (int r = 0; r < splits; ++r) m = fmaxf(m, sm.c_ml[r][0]);
         float l = 0.f, acc = 0.f;
         for (int r = 0; r < splits; ++r) {
-            const float* rml = cluster.map_shared_rank(sm.c_ml, r);
-            const float* racc = cluster.map_shared_rank(sm.c_acc, r);
-            const float c = __expf(rml[0] - m);
-            l += rml[1] * c;
-            acc += racc[tid] * c;
+            const float c = __expf(sm.c_ml[r][0] - m);
+            l += sm.c_ml[r][1] * c;
+            acc += sm.c_acc[r][tid] * c;
         }
         a.ctx[(size_t)b * inner + (size_t)h * D + tid] = __float2half(acc * __fdividef(1.0f, l + 1e-6f));
     }
-    cluster.sync();  // keep every CTA's shared memory alive until rank 0 has read it
 }
 
 // Prefill self-attention, causal with optional left padding (LLaMA) or ALiBi bias (Baichuan-13B).
