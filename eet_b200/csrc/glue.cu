@@ -137,7 +137,6 @@ rmsnorm_finalize_kernel(float* __restrict__ sums, const __half* __restrict__ sca
                         float eps)
 {
     __shared__ float red[32];
-    __shared__ float s_inv;
     pdl_launch_dependents();
     const int row = blockIdx.x;
     const int nv = n >> 3;
@@ -180,13 +179,10 @@ rmsnorm_finalize_kernel(float* __restrict__ sums, const __half* __restrict__ sca
     ss = warp_sum(ss);
     if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
     __syncthreads();
-    if (threadIdx.x < 32) {
-        float t = (threadIdx.x < (blockDim.x >> 5)) ? red[threadIdx.x] : 0.f;
-        t = warp_sum(t);
-        if (threadIdx.x == 0) s_inv = rsqrtf(t / n + eps);
-    }
-    __syncthreads();
-    const float inv = s_inv;
+    // every warp adds the (at most 32) per-warp sums itself, in the same order: one barrier instead of two
+    float tot = (threadIdx.x & 31) < (blockDim.x >> 5) ? red[threadIdx.x & 31] : 0.f;
+    tot = warp_sum(tot);
+    const float inv = rsqrtf(tot / n + eps);
 #pragma unroll
     for (int j = 0; j < 2; ++j) {
         const int i = threadIdx.x + j * blockDim.x;
