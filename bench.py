@@ -170,12 +170,12 @@ def kernel_launches_per_step(n_layers, batch, world):
     deferred_max = 16 if world > 1 else 64
     if batch <= deferred_max:
         # per layer: rmsnorm(+finalize), qkv gemm, decode attention, out gemm, rmsnorm(+finalize), gate+up gemm,
-        # swiglu(+finalize), down gemm; per step: advance_steps + final rmsnorm(+finalize)
-        return 8 * n_layers + 2
+        # swiglu(+finalize), down gemm; per step: advance_steps, embedding gather, final rmsnorm(+finalize), argmax
+        return 8 * n_layers + 4
     # larger batches: every projection is an accumulate + finalize pair, gate and up are separate launches
     # (and with tensor parallelism the residual is added by its own kernel after the NCCL all-reduce)
     per_layer = 14 + (2 if world > 1 else 0)
-    return per_layer * n_layers + 2
+    return per_layer * n_layers + 4
 
 
 # ------------------------------------------------------------------------------------------------ GEMM timing

@@ -239,6 +239,30 @@ def gemm_w8a16_accum(x, packed_w, sums, packed_w2=None, sums2=None):
                                    None if sums2 is None else sums2.data_ptr(), _stream()))
 
 
+def argmax_rows(logits2d):
+    """Greedy token choice: [rows] int64 index of the largest value of each row of a CUDA fp16 matrix (the
+    smallest index on ties, like torch.argmax); rows may be strided."""
+    rows, n = logits2d.shape
+    if logits2d.dtype != torch.float16 or not logits2d.is_cuda or logits2d.stride(1) != 1:
+        raise RuntimeError("argmax_rows: a CUDA fp16 matrix with contiguous rows is required")
+    out = torch.empty(rows, dtype=torch.int64, device=logits2d.device)
+    check(lib.eet_argmax_rows(logits2d.data_ptr(), out.data_ptr(), rows, n, logits2d.stride(0) if rows > 1 else n,
+                              _stream()))
+    return out
+
+
+def gather_rows(table, ids, out=None):
+    """Token-embedding lookup: out[..., :] = table[ids[...]] for a CUDA fp16 table [V, n] and int64 ids."""
+    V, n = table.shape
+    if table.dtype != torch.float16 or not table.is_cuda or not table.is_contiguous():
+        raise RuntimeError("gather_rows: a contiguous CUDA fp16 table is required")
+    flat = ids.reshape(-1).to(device=table.device, dtype=torch.int64).contiguous()
+    if out is None:
+        out = torch.empty((flat.numel(), n), dtype=torch.float16, device=table.device)
+    check(lib.eet_gather_rows(table.data_ptr(), flat.data_ptr(), out.data_ptr(), flat.numel(), n, V, _stream()))
+    return out.view(*ids.shape, n)
+
+
 # ---------------------------------------------------------------------------------------------------
 # deferred epilogues (decode fast path)
 # ---------------------------------------------------------------------------------------------------

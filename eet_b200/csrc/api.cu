@@ -386,4 +386,18 @@ int eet_advance_steps(int* steps, int count, int delta, void* stream)
     return launch_advance_steps(steps, count, delta, (cudaStream_t)stream);
 }
 
+int eet_argmax_rows(const void* logits, int64_t* out, int rows, int n, size_t row_stride, void* stream)
+{
+    EET_CHECK(rows >= 0 && n > 0 && (rows == 0 || (logits && out)), "eet_argmax_rows: bad arguments");
+    EET_CHECK(aligned16(logits) && row_stride % 8 == 0, "eet_argmax_rows: rows must be 16-byte aligned");
+    return launch_argmax_rows((const __half*)logits, out, rows, n, row_stride, (cudaStream_t)stream);
+}
+
+int eet_gather_rows(const void* table, const int64_t* ids, void* out, int rows, int n, int64_t rows_in_table, void* stream)
+{
+    EET_CHECK(rows >= 0 && n > 0 && rows_in_table > 0 && (rows == 0 || (table && ids && out)), "eet_gather_rows: bad arguments");
+    EET_CHECK(aligned16(table) && aligned16(out), "eet_gather_rows: pointers must be 16-byte aligned");
+    return launch_gather_rows((const __half*)table, ids, (__half*)out, rows, n, rows_in_table, (cudaStream_t)stream);
+}
+
 }  // extern "C"

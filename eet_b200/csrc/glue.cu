@@ -506,6 +506,79 @@ scatter_kv_kernel(__half* __restrict__ kcache, __half* __restrict__ vcache, int 
     reinterpret_cast<uint4*>(vcache)[dst] = ws[per_cache_vec + src];
 }
 
+// Greedy token choice: index of the largest of n fp16 logits per row, the smallest index on ties (what
+// torch.argmax returns for the reference's generation loop, python/eet/pipelines/generation.py:1185-1190).
+// One CTA per row; NaN compares false and is never chosen unless the whole row is NaN (index 0).
+__global__ void __launch_bounds__(256)
+argmax_rows_kernel(const __half* __restrict__ logits, int64_t* __restrict__ out, int n, size_t row_stride)
+{
+    __shared__ float s_val[8];
+    __shared__ int s_idx[8];
+    pdl_launch_dependents();
+    pdl_wait();
+    const __half* row = logits + (size_t)blockIdx.x * row_stride;
+    float best = -INFINITY;
+    int best_i = 0x7fffffff;
+    const int nv = n >> 3;
+    for (int i = threadIdx.x; i < nv; i += blockDim.x) {
+        const uint4 v = reinterpret_cast<const uint4*>(row)[i];
+        const __half* hv = reinterpret_cast<const __half*>(&v);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const float f = __half2float(hv[e]);
+            if (f > best) {   // strictly greater: the first (smallest) index of a maximum stays
+                best = f;
+                best_i = i * 8 + e;
+            }
+        }
+    }
+    for (int i = nv * 8 + threadIdx.x; i < n; i += blockDim.x) {   // tail when n is not a multiple of 8
+        const float f = __half2float(row[i]);
+        if (f > best) {
+            best = f;
+            best_i = i;
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+        if (ov > best || (ov == best && oi < best_i)) {
+            best = ov;
+            best_i = oi;
+        }
+    }
+    if ((threadIdx.x & 31) == 0) {
+        s_val[threadIdx.x >> 5] = best;
+        s_idx[threadIdx.x >> 5] = best_i;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < (int)(blockDim.x >> 5); ++w) {
+            if (s_val[w] > best || (s_val[w] == best && s_idx[w] < best_i)) {
+                best = s_val[w];
+                best_i = s_idx[w];
+            }
+        }
+        out[blockIdx.x] = (best_i == 0x7fffffff) ? 0 : best_i;
+    }
+}
+
+// out[r] = table[ids[r]] for rows of n fp16 values (n a multiple of 8): the token-embedding lookup that the
+// reference leaves to torch.nn.Embedding (python/eet/transformers/modeling_llama.py:281-283).
+__global__ void __launch_bounds__(256)
+gather_rows_kernel(const __half* __restrict__ table, const int64_t* __restrict__ ids, __half* __restrict__ out, int n,
+                   int64_t rows_in_table)
+{
+    pdl_launch_dependents();
+    pdl_wait();
+    int64_t id = ids[blockIdx.x];
+    if (id < 0 || id >= rows_in_table) id = 0;   // never read outside the table
+    const uint4* src = reinterpret_cast<const uint4*>(table + (size_t)id * n);
+    uint4* dst = reinterpret_cast<uint4*>(out + (size_t)blockIdx.x * n);
+    for (int i = threadIdx.x; i < (n >> 3); i += blockDim.x) dst[i] = src[i];
+}
+
 __global__ void advance_steps_kernel(int* steps, int count, int delta)
 {
     pdl_launch_dependents();
@@ -654,6 +727,22 @@ int launch_reorder_kv(__half* kcache, __half* vcache, const int64_t* index, int 
     scatter_kv_kernel<<<grid, 256, 0, stream>>>(kcache, vcache, H, T_max, step, rowvec, (const uint4*)ws,
                                                 per_cache_vec);
     EET_LAUNCH_CHECK();
+    return 0;
+}
+
+int launch_argmax_rows(const __half* logits, int64_t* out, int rows, int n, size_t row_stride, cudaStream_t stream)
+{
+    if (rows == 0) return 0;
+    EET_CUDA(launch_pdl(argmax_rows_kernel, dim3(rows), dim3(256), 0, stream, logits, out, n, row_stride));
+    return 0;
+}
+
+int launch_gather_rows(const __half* table, const int64_t* ids, __half* out, int rows, int n, int64_t rows_in_table,
+                       cudaStream_t stream)
+{
+    EET_CHECK(n % 8 == 0, "gather_rows: row length %d must be a multiple of 8", n);
+    if (rows == 0) return 0;
+    EET_CUDA(launch_pdl(gather_rows_kernel, dim3(rows), dim3(256), 0, stream, table, ids, out, n, rows_in_table));
     return 0;
 }
 

@@ -60,6 +60,9 @@ int launch_qkv_split_store(const __half* qkv, __half* q_out, __half* kcache, __h
 int launch_reorder_kv(__half* kcache, __half* vcache, const int64_t* index, int B, int H, int D, int T_max, int step,
                       __half* ws, cudaStream_t stream);
 int launch_advance_steps(int* steps, int count, int delta, cudaStream_t stream);
+int launch_argmax_rows(const __half* logits, int64_t* out, int rows, int n, size_t row_stride, cudaStream_t stream);
+int launch_gather_rows(const __half* table, const int64_t* ids, __half* out, int rows, int n, int64_t rows_in_table,
+                       cudaStream_t stream);
 
 // attention.cu
 struct DecodeAttnArgs {

@@ -266,6 +266,16 @@ class _ModelBase:
     def _bias(self, first_pass, seq_len, like):
         return _EMPTY
 
+    def _embed(self, input_ids):
+        """Token embeddings [B, S, hidden] into a pooled buffer (the reference calls torch.nn.Embedding,
+        modeling_llama.py:281-283; this is the same lookup as one small kernel of this library, which also
+        takes part in the programmatic launch chain of a decode step)."""
+        B, S = input_ids.shape
+        h = self.config.hidden_size
+        cap = self.max_batch * self.max_prompt_len
+        buf = EET._pool.get("embed_out", cap * h, torch.float16, self.desc.device)[: B * S * h].view(B * S, h)
+        return EET.gather_rows(self.embedding.weight, input_ids, out=buf).view(B, S, h)
+
     def __call__(self, input_ids, first_pass=True, position_ids=None, token_type_ids=None, attention_mask=None,
                  reorder_state=None, context_lengths=None):
         shape = input_ids.size()
@@ -279,7 +289,7 @@ class _ModelBase:
             pre_padding_len = torch.sum(1 - attention_mask, 1, True).to(self.desc.device).long()
         if reorder_state is not None:
             self.reorder_state = reorder_state.long()
-        x = self.embedding(input_ids)
+        x = self._embed(input_ids)
         self.past_kv_length += shape[1]
         bias = self._bias(first_pass, self.past_kv_length, x)
         for layer in self.layers:
@@ -383,7 +393,7 @@ class _CausalLMBase:
         # inside the kernel that consumes it
         with EET.deferred_epilogue():
             hidden = self.model(input_ids=ids, first_pass=False)
-        return torch.argmax(self.lm_head(hidden)[:, -1, :], dim=-1, keepdim=True)
+        return EET.argmax_rows(self.lm_head(hidden)[:, -1, :]).view(-1, 1)
 
     def _capture(self, B):
         """Captures one decode step (embedding -> layers -> norm -> lm_head -> argmax) as a CUDA graph.  The

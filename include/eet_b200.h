@@ -232,6 +232,16 @@ int eet_reorder_kv(void* kcache, void* vcache, const int64_t* index, int B, int 
  * (LlamaMmha::step_, csrc/op/llama_mmha.cpp:121,195,210); this is its device-resident twin. */
 int eet_advance_steps(int* steps, int count, int delta, void* stream);
 
+/* out[r] (int64) = index of the largest of the n fp16 values of row r (rows row_stride elements apart), the
+ * smallest index on ties: the greedy token choice.  The reference leaves it to torch.argmax
+ * (python/eet/pipelines/generation.py:1185-1190). */
+int eet_argmax_rows(const void* logits, int64_t* out, int rows, int n, size_t row_stride, void* stream);
+
+/* out[r][0..n) = table[ids[r]][0..n), fp16, n a multiple of 8, ids device int64 (an id outside
+ * [0, rows_in_table) reads row 0): the token-embedding lookup, torch.nn.Embedding in the reference
+ * (python/eet/transformers/modeling_llama.py:281-283). */
+int eet_gather_rows(const void* table, const int64_t* ids, void* out, int rows, int n, int64_t rows_in_table, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -83,3 +83,23 @@ def test_reorder_kv():
     want_k[:, :, :step] = k[idx][:, :, :step]
     want_v[:, :, :step] = v[idx][:, :, :step]
     assert torch.equal(kc.cpu(), want_k) and torch.equal(vc.cpu(), want_v)
+
+
+def test_argmax_rows_and_gather_rows():
+    """Greedy token choice and embedding lookup: equal to torch.argmax (first index on ties) / table[ids]."""
+    from eet_b200 import EET
+    gen = torch.Generator().manual_seed(41)
+    logits = torch.randn(5, 32008, generator=gen).half().cuda()[:, :32003]   # rows 16-byte aligned, ragged length
+    logits[1, 17] = logits[1, 30000] = 60000.0          # a tie: the smaller index wins
+    logits[2, :] = -3.0                                  # all equal: index 0
+    logits[3, 32002] = 50000.0                           # the maximum in the ragged tail (n % 8 != 0)
+    got = EET.argmax_rows(logits)
+    assert got.dtype == torch.int64 and got.tolist() == [int(logits[0].float().argmax()), 17, 0, 32002,
+                                                         int(logits[4].float().argmax())]
+    # strided rows, as lm_head(hidden)[:, -1, :] hands them over
+    big = torch.randn(3, 4, 1000, generator=gen).half().cuda()
+    view = big[:, -1, :]
+    assert torch.equal(EET.argmax_rows(view), view.float().argmax(-1))
+    table = torch.randn(50, 256, generator=gen).half().cuda()
+    ids = torch.tensor([[3, 49], [0, 7]]).cuda()
+    assert torch.equal(EET.gather_rows(table, ids), table[ids])
