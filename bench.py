@@ -388,7 +388,7 @@ def run_ours(args):
     # ---- region 1: end to end through the public API, ids from pinned host memory, tokens read back ----
     host_ids.copy_(first.cpu())
     for _ in range(W):
-        nxt = model.decode_step(host_ids.to(dev, non_blocking=True))
+        nxt = model.decode_step(host_ids)
         host_next.copy_(nxt, non_blocking=True)
         torch.cuda.synchronize()
         host_ids.copy_(host_next)
@@ -397,7 +397,7 @@ def run_ours(args):
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         for _ in range(K):
-            nxt = model.decode_step(host_ids.to(dev, non_blocking=True))
+            nxt = model.decode_step(host_ids)
             host_next.copy_(nxt, non_blocking=True)
             torch.cuda.current_stream().synchronize()
             host_ids.copy_(host_next)

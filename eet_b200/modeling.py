@@ -422,17 +422,20 @@ class _CausalLMBase:
         self._graph = g
 
     def decode_step(self, ids):
-        """One greedy decode step for ids [B, 1] (device int64): returns the next ids [B, 1].  With
-        use_cuda_graph the step is captured on its second use and replayed afterwards."""
+        """One greedy decode step for ids [B, 1] (int64, on the device or in host memory): returns the next ids
+        [B, 1] on the device.  With use_cuda_graph the step is captured on its second use and replayed
+        afterwards."""
         m = self.model
+        dev = m.desc.device
         if not self.use_cuda_graph or m.reorder_state.numel() != 0:
-            return self._decode_eager(ids, None)
+            return self._decode_eager(ids.to(dev, non_blocking=True), None)
         B = ids.shape[0]
         if self._graph is None or self._graph["B"] != B:
             if not getattr(self, "_warmed", False):
                 self._warmed = True
-                return self._decode_eager(ids, None)   # first step eagerly: sizes every pooled buffer
+                return self._decode_eager(ids.to(dev, non_blocking=True), None)   # first step eagerly: sizes every pooled buffer
             self._capture(B)
+        # ids may live in (pinned) host memory: they are copied straight into the graph's input tensor
         g = self._graph
         g["ids"].copy_(ids, non_blocking=True)
         g["graph"].replay()
