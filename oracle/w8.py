@@ -104,7 +104,7 @@ def b200_unpack_int8(packed: np.ndarray) -> np.ndarray:
 # --------------------------------------------------------------------------- checking libraries
 def build(target: str = "all", quiet: bool = True) -> None:
     """Runs the Makefile beside this file ('oracle', 'ref' or 'all').  'ref' needs the reference checkout
-    (REF=/root/reference by default) and is skipped silently by callers when it is absent."""
+    (the Makefile's REF variable) and is skipped silently by callers when it is absent."""
     subprocess.run(["make", "-C", HERE, target], check=True,
                    stdout=subprocess.DEVNULL if quiet else None, stderr=subprocess.DEVNULL if quiet else None)
 

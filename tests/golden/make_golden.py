@@ -1,5 +1,5 @@
 """Generates the golden fixtures of this folder from the reference itself.  Run on a machine that has
-the reference checkout (default /root/reference):
+the reference checkout (environment variable EET_REFERENCE):
 
     make -C oracle ref && python tests/golden/make_golden.py
 
