@@ -310,6 +310,39 @@ def cpu_decode_sample(steps, layers=1, threads=None):
     return tok_s, threads, sample, dt
 
 
+def profile_kernels():
+    """A handful of launches for profiler captures of the tensor-core kernels (`--profile-kernels`): the stream-K
+    kernel at M = 32 and M = 256 on K=8192, N=22016, the 256 x 256 tile kernel at M = 4096 on K=4096, N=11008,
+    and the prefill attention at B=8, H=32, S=512.  Every working set exceeds L2; nothing is timed or printed
+    but the device status."""
+    from eet_b200 import EET, _lib
+    from eet_b200._lib import check, lib
+    dev = torch.device("cuda", 0)
+
+    def gemm(K, N, M, reps=2):
+        w = torch.randint(-128, 128, (K, N), dtype=torch.int8, device=dev)
+        s = (torch.rand(N, device=dev) * 1e-3).half()
+        x = torch.randn(M, K, device=dev).half()
+        out = torch.empty(M, N, device=dev, dtype=torch.float16)
+        for _ in range(reps):
+            EET.gemm_w8a16(x, w, s, out=out)
+        torch.cuda.synchronize()
+
+    gemm(8192, 22016, 32)
+    gemm(8192, 22016, 256)
+    gemm(4096, 11008, 4096)
+    B, H, S, D, T = 8, 32, 512, 128, 640
+    q = torch.randn(B, H, S, D, device=dev).half()
+    k = torch.randn(B, H, T, D, device=dev).half()
+    v = torch.randn(B, H, T, D, device=dev).half()
+    ctx = torch.empty(B, S, H * D, device=dev, dtype=torch.float16)
+    st = torch.cuda.current_stream().cuda_stream
+    for _ in range(2):
+        check(lib.eet_prefill_mha(q.data_ptr(), k.data_ptr(), v.data_ptr(), ctx.data_ptr(), B, S, H, D, T, None, None, S, st))
+    torch.cuda.synchronize()
+    print(json.dumps({"profile_kernels": "done", "device_status": _lib.device_status()}))
+
+
 # ------------------------------------------------------------------------------------------------ arms
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
@@ -492,13 +525,17 @@ def main():
     ap.add_argument("--no-graph", action="store_true", help="launch the decode step eagerly")
     ap.add_argument("--no-sweep", action="store_true", help="skip the GEMM sweep")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline")
+    ap.add_argument("--profile-kernels", action="store_true",
+                    help="run a few launches of the tensor-core kernels for a profiler capture and exit")
     ap.add_argument("--skip-prefill", action="store_true",
                     help="fill the KV cache with random data instead of running the prompt (profiling runs only)")
     args = ap.parse_args()
     select_workload(args.workload)
     if args.warmup < 3:
         args.warmup = 3
-    if args.impl == "reference":
+    if args.profile_kernels:
+        profile_kernels()
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)
