@@ -238,7 +238,7 @@ rmsnorm_finalize_tp_kernel(TpPeers peers, float* __restrict__ local_sums, int* _
     namespace cgx = cooperative_groups;
     cgx::cluster_group cluster = cgx::this_cluster();
     __shared__ float red[32];
-    __shared__ float s_part;     // this CTA's share of the row's sum of squares, read by the cluster
+    __shared__ float s_parts[8]; // every CTA's share of the row's sum of squares, written by the owners
     __shared__ int s_epoch;
     pdl_launch_dependents();
     const int slices = (int)cluster.num_blocks();
@@ -328,11 +328,13 @@ rmsnorm_finalize_tp_kernel(TpPeers peers, float* __restrict__ local_sums, int* _
     if (threadIdx.x < 32) {
         float t = (threadIdx.x < (blockDim.x >> 5)) ? red[threadIdx.x] : 0.f;
         t = warp_sum(t);
-        if (threadIdx.x == 0) s_part = t;
+        // this CTA's share goes into EVERY CTA's shared memory (lane c writes to CTA c): after the cluster
+        // barrier each CTA adds the shares from its own memory and nobody touches a peer's any more
+        if ((int)threadIdx.x < slices) *cluster.map_shared_rank(&s_parts[slice], threadIdx.x) = t;
     }
-    cluster.sync();   // every CTA's share is written (and every CTA has read the old epoch counter)
+    cluster.sync();   // every share is written (and every CTA has read the old epoch counter)
     float total = 0.f;
-    for (int c = 0; c < slices; ++c) total += *cluster.map_shared_rank(&s_part, c);   // same order in every CTA
+    for (int c = 0; c < slices; ++c) total += s_parts[c];   // same order in every CTA
     if (slice == 0 && threadIdx.x == 0) epochs[peers.which * kTpRows + row] = (int)epoch;
     const float inv = rsqrtf(total / n + eps);
     {
@@ -347,7 +349,6 @@ rmsnorm_finalize_tp_kernel(TpPeers peers, float* __restrict__ local_sums, int* _
         }
         reinterpret_cast<uint4*>(xn_out + (size_t)row * n)[i] = o;
     }
-    cluster.sync();   // no CTA leaves while its shared memory may still be read by the others
 }
 
 // gate <- up * gate / (1 + exp(-gate)) with the reference's mix of precisions: exp in fp32 rounded to
