@@ -58,7 +58,7 @@ extern "C" {
 
 int eet_abi_version(void)
 {
-    return 2;
+    return 3;
 }
 
 const char* eet_last_error(void)

@@ -20,7 +20,7 @@
 extern "C" {
 #endif
 
-/* ABI version of this header; bumped when a signature changes. */
+/* ABI version of this header (3); bumped when a signature changes. */
 int eet_abi_version(void);
 
 /* Message of the last failure on the calling thread ("" if none). */
