@@ -389,7 +389,6 @@ int eet_advance_steps(int* steps, int count, int delta, void* stream)
 int eet_argmax_rows(const void* logits, int64_t* out, int rows, int n, size_t row_stride, void* stream)
 {
     EET_CHECK(rows >= 0 && n > 0 && (rows == 0 || (logits && out)), "eet_argmax_rows: bad arguments");
-    EET_CHECK(aligned16(logits) && row_stride % 8 == 0, "eet_argmax_rows: rows must be 16-byte aligned");
     return launch_argmax_rows((const __half*)logits, out, rows, n, row_stride, (cudaStream_t)stream);
 }
 

@@ -511,7 +511,7 @@ scatter_kv_kernel(__half* __restrict__ kcache, __half* __restrict__ vcache, int 
 // torch.argmax returns for the reference's generation loop, python/eet/pipelines/generation.py:1185-1190).
 // One CTA per row; NaN compares false and is never chosen unless the whole row is NaN (index 0).
 __global__ void __launch_bounds__(256)
-argmax_rows_kernel(const __half* __restrict__ logits, int64_t* __restrict__ out, int n, size_t row_stride)
+argmax_rows_kernel(const __half* __restrict__ logits, int64_t* __restrict__ out, int n, size_t row_stride, int vec_ok)
 {
     __shared__ float s_val[8];
     __shared__ int s_idx[8];
@@ -520,7 +520,7 @@ argmax_rows_kernel(const __half* __restrict__ logits, int64_t* __restrict__ out,
     const __half* row = logits + (size_t)blockIdx.x * row_stride;
     float best = -INFINITY;
     int best_i = 0x7fffffff;
-    const int nv = n >> 3;
+    const int nv = vec_ok ? (n >> 3) : 0;   // 16-byte loads only when every row is 16-byte aligned
     for (int i = threadIdx.x; i < nv; i += blockDim.x) {
         const uint4 v = reinterpret_cast<const uint4*>(row)[i];
         const __half* hv = reinterpret_cast<const __half*>(&v);
@@ -533,7 +533,7 @@ argmax_rows_kernel(const __half* __restrict__ logits, int64_t* __restrict__ out,
             }
         }
     }
-    for (int i = nv * 8 + threadIdx.x; i < n; i += blockDim.x) {   // tail when n is not a multiple of 8
+    for (int i = nv * 8 + threadIdx.x; i < n; i += blockDim.x) {   // tail, or everything for unaligned rows
         const float f = __half2float(row[i]);
         if (f > best) {
             best = f;
@@ -734,7 +734,8 @@ int launch_reorder_kv(__half* kcache, __half* vcache, const int64_t* index, int 
 int launch_argmax_rows(const __half* logits, int64_t* out, int rows, int n, size_t row_stride, cudaStream_t stream)
 {
     if (rows == 0) return 0;
-    EET_CUDA(launch_pdl(argmax_rows_kernel, dim3(rows), dim3(256), 0, stream, logits, out, n, row_stride));
+    const int vec_ok = (reinterpret_cast<uintptr_t>(logits) % 16 == 0 && row_stride % 8 == 0) ? 1 : 0;
+    EET_CUDA(launch_pdl(argmax_rows_kernel, dim3(rows), dim3(256), 0, stream, logits, out, n, row_stride, vec_ok));
     return 0;
 }
 

@@ -100,6 +100,8 @@ def test_argmax_rows_and_gather_rows():
     big = torch.randn(3, 4, 1000, generator=gen).half().cuda()
     view = big[:, -1, :]
     assert torch.equal(EET.argmax_rows(view), view.float().argmax(-1))
+    odd = torch.randn(3, 1001, generator=gen).half().cuda()       # rows not 16-byte aligned: scalar path
+    assert torch.equal(EET.argmax_rows(odd), odd.float().argmax(-1))
     table = torch.randn(50, 256, generator=gen).half().cuda()
     ids = torch.tensor([[3, 49], [0, 7]]).cuda()
     assert torch.equal(EET.gather_rows(table, ids), table[ids])
