@@ -24,7 +24,7 @@ from ._lib import EETError, check, lib
 
 __all__ = ["MetaDesc", "LlamaMmha", "BaichuanMmha", "GatedFeedForwardNetworkInt8", "LayerNorm", "quant_weights",
            "preprocess_weights", "unpack_weights", "repack_reference_weights", "gemm_w8a16", "gemm_w8a16_accum",
-           "deferred_epilogue", "EETError"]
+           "deferred_epilogue", "check_device_status", "EETError"]
 
 
 def _stream():
@@ -93,6 +93,15 @@ class _Pool:
         self.buffers.clear()
         self.gemm_ws.clear()
 
+    def rezero(self):
+        """Puts every buffer that the kernels expect to find zero (the fp32 sum buffers, the split-K scratch) back
+        to zero: what a kernel that gave up on a wait left in them is undefined."""
+        for key, buf in self.buffers.items():
+            if key[0].startswith("z:"):
+                buf.zero_()
+        for buf in self.gemm_ws.values():
+            buf.zero_()
+
 
 _pool = _Pool()
 
@@ -100,6 +109,33 @@ _pool = _Pool()
 def clear_buffers():
     """Drops the pooled scratch buffers (MManager::clear, csrc/op/mmanager.hpp:211-214)."""
     _pool.clear()
+
+
+_STATUS_TEXT = {
+    1: "decode GEMM: a shared-memory pipeline wait ran out",
+    2: "tensor-core GEMM: a pipeline or tensor-memory wait ran out",
+    3: "decode attention: a pipeline wait ran out",
+    4: "tensor-parallel exchange: a peer's partial sums never arrived",
+    5: "decode attention: the step ran past the end of the KV cache",
+    6: "layer-chain kernel: a grid-wide barrier ran out",
+}
+
+
+def check_device_status(tp=None):
+    """Reads the device-side status word (synchronises the device).  If a kernel gave up since the last check,
+    the pooled fp32 scratch is put back to zero - every later GEMM would otherwise add onto what the failed
+    kernel left there - the deferred-output table is dropped, and EETError is raised, as the reference raises
+    from check_cuda_error at its next synchronisation point (csrc/op/common.hpp:55-64).  With tensor
+    parallelism pass the handle: this rank's peer buffers are cleared as well; the other ranks must do the
+    same (TensorParallel.reset_peer_buffers is collective) before the group decodes again."""
+    status = _lib.device_status()
+    if status == 0:
+        return
+    _pending.clear()
+    _pool.rezero()
+    if tp is not None and getattr(tp, "_peer", None) is not None:
+        tp._peer.clear_local()
+    raise EETError(f"device status {status}: {_STATUS_TEXT.get(status, 'unknown code')}; scratch buffers were re-zeroed")
 
 
 # ---------------------------------------------------------------------------------------------------

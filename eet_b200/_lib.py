@@ -17,6 +17,7 @@ SIGNATURES = {
     "eet_abi_version": (_i, []),
     "eet_last_error": (_c.c_char_p, []),
     "eet_device_status": (_i, [_c.POINTER(_i)]),
+    "eet_set_wait_limit": (_i, [_c.c_uint]),
     "eet_quantize_w8_workspace_bytes": (_sz, [_i, _i]),
     "eet_quantize_w8": (_i, [_vp, _i, _i, _i, _vp, _vp, _vp, _i, _vp, _sz, _vp]),
     "eet_pack_w8": (_i, [_vp, _i, _i, _vp, _vp]),

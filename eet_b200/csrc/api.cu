@@ -58,7 +58,7 @@ extern "C" {
 
 int eet_abi_version(void)
 {
-    return 3;
+    return 4;
 }
 
 const char* eet_last_error(void)
@@ -76,6 +76,13 @@ int eet_device_status(int* status_out)
         EET_CUDA(cudaMemcpyToSymbol(g_device_status, &zero, sizeof(int)));
     }
     *status_out = v;
+    return 0;
+}
+
+int eet_set_wait_limit(unsigned int polls)
+{
+    EET_CHECK(polls >= 1, "eet_set_wait_limit: the limit must be at least 1");
+    EET_CUDA(cudaMemcpyToSymbol(g_wait_limit, &polls, sizeof(polls)));
     return 0;
 }
 

@@ -138,7 +138,16 @@ decode_mha_kernel(DecodeAttnArgs a)
     // everything this kernel reads that an earlier kernel of the same step produced (the projection of the
     // new token, the device-resident step) comes after this wait
     pdl_wait();
-    const int step = a.step_dev ? *a.step_dev : a.step;
+    int step = a.step_dev ? *a.step_dev : a.step;
+    // A device-resident step is not seen by the host-side range check.  Outside [1, T_max] the append would land in
+    // another head's cache (or past the allocation) and the tile sizes below would go negative: record status 5,
+    // touch no cache row and request no tile; every CTA still walks the same path to the cluster barrier and the
+    // context of this (batch, head) comes out as zeros.
+    const bool step_ok = (step >= 1 && step <= a.T_max);
+    if (!step_ok) {
+        if (tid == 0) g_device_status = 5;
+        step = 1;
+    }
     const size_t inner = (size_t)a.H * D;
 
     // ---- slice of the history owned by this CTA: equal numbers of time steps (not of tiles: with 580 steps
@@ -149,7 +158,7 @@ decode_mha_kernel(DecodeAttnArgs a)
     int pad = 0;
     if (a.pad_len != nullptr) pad = (int)a.pad_len[b];
     const int t_first = max(t_begin, pad / kAttnTile * kAttnTile);  // whole tiles left of the padding are skipped
-    const int n_tiles = (t_end > t_first) ? (t_end - t_first + kAttnTile - 1) / kAttnTile : 0;
+    const int n_tiles = (step_ok && t_end > t_first) ? (t_end - t_first + kAttnTile - 1) / kAttnTile : 0;
     const size_t cache_row0 = ((size_t)b * a.H + h) * a.T_max;
 
     if (warp == kAttnConsumerWarps) {
@@ -166,6 +175,7 @@ decode_mha_kernel(DecodeAttnArgs a)
                 const int t = t_first + j * kAttnTile;
                 // rows up to the cache end may be copied: rows at or beyond `step` are never used
                 const int rows = min(kAttnTile, a.T_max - t);
+                if (rows <= 0) break;   // cannot happen for a step inside the cache; never hand the copy engine a negative size
                 uint8_t* dst = attn_dyn + (size_t)s * kAttnStageBytes;
                 mbar_arrive_expect_tx(&sm.full[s], (uint32_t)(2 * rows * kAttnRowBytes));
                 bulk_g2s(dst, a.kcache + (cache_row0 + t) * D, (uint32_t)(rows * kAttnRowBytes), &sm.full[s]);
@@ -213,7 +223,7 @@ decode_mha_kernel(DecodeAttnArgs a)
         asm volatile("bar.sync 1, %0;" ::"n"(kAttnConsumerThreads) : "memory");
 
         // cache append: done by the CTA whose slice holds the newest position
-        if (step - 1 >= t_begin && step - 1 < t_end && tid < 32) {
+        if (step_ok && step - 1 >= t_begin && step - 1 < t_end && tid < 32) {
             uint4* kd = reinterpret_cast<uint4*>(a.kcache + (cache_row0 + step - 1) * D);
             uint4* vd = reinterpret_cast<uint4*>(a.vcache + (cache_row0 + step - 1) * D);
             if (tid < 16) {

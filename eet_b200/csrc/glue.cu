@@ -216,7 +216,6 @@ struct TpPeers {
     int world, rank, which;
 };
 
-constexpr uint32_t kTpSpinLimit = 1u << 22;
 constexpr int kTpRows = 16;
 
 __device__ __forceinline__ uint4 ld_volatile_u4(const void* p)
@@ -248,6 +247,7 @@ rmsnorm_finalize_tp_kernel(TpPeers peers, float* __restrict__ local_sums, int* _
     const uint4 sc = reinterpret_cast<const uint4*>(scale)[slice * blockDim.x + threadIdx.x];
     const uint4 g = reinterpret_cast<const uint4*>(gamma)[slice * blockDim.x + threadIdx.x];
     pdl_wait();   // this rank's GEMM (and everything before it) is complete
+    const uint32_t spin_limit = g_wait_limit;
     // every CTA of the row derives the epoch from the counter; the row's first CTA advances it afterwards
     if (threadIdx.x == 0) s_epoch = epochs[peers.which * kTpRows + row] + 1;
     __syncthreads();
@@ -301,7 +301,7 @@ rmsnorm_finalize_tp_kernel(TpPeers peers, float* __restrict__ local_sums, int* _
 #pragma unroll
             for (int e = 0; e < 4; ++e) ok = ok && c[e].y == epoch && c[e].w == epoch;
             if (ok) break;
-            if (++spins > kTpSpinLimit) {
+            if (++spins > spin_limit) {
                 g_device_status = 4;   // a peer never arrived: give up, the host reads the status word
                 break;
             }
@@ -649,7 +649,9 @@ int launch_rmsnorm_finalize_tp(float* local_sums, void* const* peer_inbox, int w
     const int nv = n / 8;
     int slices = 8;
     while (slices > 1 && (nv % (slices * 32) != 0 || nv / slices > 1024)) slices >>= 1;
-    EET_CHECK(nv % slices == 0 && nv / slices <= 1024, "tensor-parallel rmsnorm: hidden size %d is not supported", n);
+    // whole warps only: the block reductions shuffle with the full mask
+    EET_CHECK(nv % slices == 0 && (nv / slices) % 32 == 0 && nv / slices <= 1024,
+              "tensor-parallel rmsnorm: hidden size %d is not supported (a multiple of 256 up to 65536 is required)", n);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)(M * slices));
     cfg.blockDim = dim3((unsigned)(nv / slices));

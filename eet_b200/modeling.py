@@ -395,6 +395,13 @@ class _CausalLMBase:
             hidden = self.model(input_ids=ids, first_pass=False)
         return EET.argmax_rows(self.lm_head(hidden)[:, -1, :]).view(-1, 1)
 
+    def decode_logits(self, ids):
+        """Logits [B, 1, vocab] of one decode step for ids [B, 1], computed by the same chain of kernels that
+        decode_step() and generate() run (deferred epilogues, fused tensor-parallel exchange), eagerly."""
+        with EET.deferred_epilogue():
+            hidden = self.model(input_ids=ids, first_pass=False)
+        return self.lm_head(hidden)
+
     def _capture(self, B):
         """Captures one decode step (embedding -> layers -> norm -> lm_head -> argmax) as a CUDA graph.  The
         attention ops read their step from device memory inside the graph; one extra launch at the head of
@@ -430,6 +437,10 @@ class _CausalLMBase:
         if not self.use_cuda_graph or m.reorder_state.numel() != 0:
             return self._decode_eager(ids.to(dev, non_blocking=True), None)
         B = ids.shape[0]
+        # the captured graph advances the step on the device, where no host check sees it: refuse here, before
+        # anything is launched, exactly where the eager path raises (LlamaMmha::forward_inc asserts the same)
+        if any(layer.attention.step_ + 1 > m.max_full_seq_len for layer in m.layers):
+            raise RuntimeError("Exceed the maximum step length")
         if self._graph is None or self._graph["B"] != B:
             if not getattr(self, "_warmed", False):
                 self._warmed = True
@@ -471,7 +482,9 @@ class _CausalLMBase:
             toks.append(nxt)
         if attention_mask is not None:
             self.model.pre_padding_len = torch.empty(0).long()
-        return torch.cat(toks, dim=1)
+        out = torch.cat(toks, dim=1)
+        EET.check_device_status(self.model.desc.tp)   # a kernel that gave up on a wait must not go unnoticed
+        return out
 
     @torch.no_grad()
     def beam_search(self, input_ids, num_beams, max_new_tokens):
@@ -503,6 +516,7 @@ class _CausalLMBase:
                     logits = self(ids[:, -1:].contiguous(), first_pass=False, reorder_state=reorder).logits[:, -1]
         finally:
             self.model.reorder_state = torch.empty(0).long()
+        EET.check_device_status(self.model.desc.tp)
         best = scores.argmax(-1)
         rows = torch.arange(B, device=dev)
         return ids.view(B, nb, -1)[rows, best], scores[rows, best]

@@ -29,6 +29,15 @@ class TensorParallel:
             self._peer = PeerBuffers(self, hidden, device)
         return self._peer
 
+    def reset_peer_buffers(self):
+        """Collective: every rank clears its partial sums, inbox and epoch counters, then all meet at a barrier.
+        Needed after a rank reported device status 4 (a peer's sums never arrived): the epochs of the ranks may
+        have diverged."""
+        if getattr(self, "_peer", None) is not None:
+            self._peer.clear_local()
+            torch.cuda.synchronize()
+        dist.barrier(group=self.group)
+
     def all_reduce(self, tensor):
         """In-place sum over the group on the current stream."""
         if self.size > 1:
@@ -58,23 +67,36 @@ class PeerBuffers:
         self.epochs = torch.zeros(2 * self.ROWS, dtype=torch.int32, device=device)
         torch.cuda.synchronize(device)
         everyone = [None] * tp.size
-        dist.all_gather_object(everyone, reduce_tensor(self.local_inbox), group=tp.group)
+        dist.all_gather_object(everyone, (reduce_tensor(self.local_inbox), device.index), group=tp.group)
 
-        def open_on_my_device(reduced):
+        def open_on_my_device(reduced, exporter_index):
             # The handle is opened with THIS rank's device current, so the peer's memory is mapped into this
             # device's address space (the driver enables peer access for the mapping) - the arrangement NCCL's
             # own P2P transport uses.  Opening it under the exporting device's index, which is what the stock
             # tensor rebuild does, yields a mapping that kernels running on this device cannot touch.
+            # The positional layout of torch's rebuild tuple is not a public interface: verify that the slot
+            # patched below really is the exporter's device index before touching it.
+            from torch.multiprocessing.reductions import rebuild_cuda_tensor
             fn, args = reduced
             args = list(args)
+            if fn is not rebuild_cuda_tensor or len(args) < 7 or args[6] != exporter_index:
+                raise RuntimeError("eet_b200.tp: torch's CUDA IPC rebuild arguments have an unexpected layout "
+                                   "(storage_device is not argument 6); the fused tensor-parallel exchange cannot "
+                                   "map the peers' inboxes with this torch version")
             args[6] = device.index   # storage_device
             return fn(*args)
 
-        self.inboxes = [self.local_inbox if r == tp.rank else open_on_my_device(h) for r, h in enumerate(everyone)]
+        self.inboxes = [self.local_inbox if r == tp.rank else open_on_my_device(*h) for r, h in enumerate(everyone)]
         torch.cuda.synchronize(device)
         dist.barrier(group=tp.group)
         self._n = n
         self.inbox_ptrs = (ctypes.c_void_p * tp.size)(*[t.data_ptr() for t in self.inboxes])
+
+    def clear_local(self):
+        """Zeroes this rank's partial sums, inbox and epoch counters (see TensorParallel.reset_peer_buffers)."""
+        self.local_sums.zero_()
+        self.local_inbox.zero_()
+        self.epochs.zero_()
 
     def buffer(self, which, rows):
         """This rank's partial-sum buffer 0 (attention output projection) or 1 (FFN down projection)."""

@@ -20,15 +20,30 @@
 extern "C" {
 #endif
 
-/* ABI version of this header (3); bumped when a signature changes. */
+/* ABI version of this header (4); bumped when a signature changes. */
 int eet_abi_version(void);
 
 /* Message of the last failure on the calling thread ("" if none). */
 const char* eet_last_error(void);
 
-/* Reads (and clears) the device-side status word of the current device: 0 = no kernel gave up on a
- * bounded wait since the last call.  Synchronises the device. */
+/* Reads (and clears) the device-side status word of the current device; 0 = no kernel gave up since the last
+ * call.  Every wait inside the kernels is bounded: a kernel that gives up records a code and returns normally.
+ *   1  decode GEMM: a shared-memory pipeline wait ran out
+ *   2  tensor-core GEMM: a pipeline or tensor-memory wait ran out
+ *   3  decode attention: a pipeline wait ran out
+ *   4  tensor-parallel exchange: a peer's partial sums never arrived
+ *   5  decode attention: the device-resident step was outside [1, T_max]; nothing was appended to the cache
+ *   6  layer-chain kernel: a grid-wide barrier ran out
+ * After a non-zero status the fp32 scratch buffers of the failed call hold undefined values: zero them (and, for
+ * the tensor-parallel exchange, the inboxes and epoch counters of every rank) before the next call.
+ * Synchronises the device.  The reference reports asynchronous failures the same way, at its next
+ * check_cuda_error (csrc/op/common.hpp:55-64). */
 int eet_device_status(int* status_out);
+
+/* Number of polls after which a wait on another CTA or another GPU (tensor-parallel inbox, grid barrier) gives up
+ * on the current device; the default, 1 << 22, is a second or more.  Takes effect for kernels launched after the
+ * call; synchronises the device.  No counterpart in the reference (it has no such waits). */
+int eet_set_wait_limit(unsigned int polls);
 
 /* ------------------------------------------------------------------------------------------------
  * Quantizer and packer

@@ -20,7 +20,7 @@ def test_header_symbols_are_exported_and_bound():
     for n in names:
         assert hasattr(raw, n), f"{n} is declared in include/eet_b200.h but not exported"
     assert sorted(_lib.SIGNATURES) == names, "ctypes table and header disagree"
-    assert _lib.lib.eet_abi_version() == 3
+    assert _lib.lib.eet_abi_version() == 4
 
 
 def test_argument_validation_happens_before_any_cuda_call():

@@ -12,7 +12,9 @@ import bench  # noqa: E402
 
 
 def test_reference_arm_prints_one_contract_line(monkeypatch, capsys):
-    monkeypatch.setattr(bench, "cpu_decode_sample", lambda steps, layers=1, threads=None: (1.5, 8, "stub sample", 0.16))
+    stub = {"tok_s": 1.5, "threads": 8, "sample": "stub sample", "step_s_measured": 5.12, "step_s": 5.12,
+            "layers_run": 32, "layers": 32, "steps": 4}
+    monkeypatch.setattr(bench, "cpu_decode_sample", lambda steps, warmup=1, budget_s=15.0, threads=None: dict(stub))
     monkeypatch.setenv("RANK", "0")
     bench.run_reference(types.SimpleNamespace(steps=4, warmup=3, gpus=1))
     lines = [ln for ln in capsys.readouterr().out.splitlines() if ln.strip()]
@@ -23,7 +25,31 @@ def test_reference_arm_prints_one_contract_line(monkeypatch, capsys):
     assert d["cpu_baseline"]["kind"] == "port" and d["cpu_baseline"]["cores"] == 8
     assert d["e2e"] == {"value": 1.5, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
     assert d["config"]["workload"] == bench.WORKLOAD
-    assert d["ms_per_step"] == pytest.approx(0.16 * 32 * 1e3)
+    # both arms print the same config keys, so the driver can tell that they ran the same thing
+    assert d["config"] == bench.bench_config(32, 1, True, 3, 4)
+    assert d["ms_per_step"] == pytest.approx(5120.0) and d["extrapolated"] is None
+
+
+def test_reference_arm_says_when_it_extrapolates(monkeypatch, capsys):
+    stub = {"tok_s": 1.5, "threads": 8, "sample": "stub sample", "step_s_measured": 1.28, "step_s": 5.12,
+            "layers_run": 8, "layers": 32, "steps": 128}
+    monkeypatch.setattr(bench, "cpu_decode_sample", lambda *a, **k: dict(stub))
+    monkeypatch.setenv("RANK", "0")
+    bench.run_reference(types.SimpleNamespace(steps=128, warmup=3, gpus=1))
+    d = json.loads(capsys.readouterr().out.strip())
+    assert d["extrapolated"] == {"layers_run": 8, "factor": 4.0, "ms_per_step_measured": 1280.0}
+
+
+def test_cpu_sample_runs_every_layer_when_the_budget_allows(monkeypatch):
+    """The sample itself, on a toy architecture so that it takes a moment: all layers run, nothing is scaled."""
+    monkeypatch.setattr(bench, "CFG", dict(bench.CFG, hidden_size=256, num_attention_heads=2, intermediate_size=512,
+                                           num_hidden_layers=3))
+    monkeypatch.setattr(bench, "PROMPT", 8)
+    monkeypatch.setattr(bench, "BATCH", 2)
+    r = bench.cpu_decode_sample(2, warmup=1, budget_s=60.0, threads=2)
+    assert r["layers_run"] == 3 and r["layers"] == 3 and r["step_s"] == r["step_s_measured"] and r["tok_s"] > 0
+    r = bench.cpu_decode_sample(2, warmup=1, budget_s=0.0, threads=2)
+    assert r["layers_run"] == 1 and r["step_s"] == pytest.approx(3 * r["step_s_measured"])
 
 
 def test_reference_arm_is_silent_on_other_ranks(monkeypatch, capsys):

@@ -227,3 +227,31 @@ def test_large_m_tensor_core_kernels(KNM):
     yr = _run(x, q, s, residual=res)
     # (M <= 512 sums with atomics: two runs may differ in the last fp16 bit)
     assert torch.allclose(yr[rows].float(), ops.add_residual(y[rows], res[rows]).float(), rtol=2e-3, atol=2e-3)
+
+
+@pytest.mark.parametrize("M", [64, 256, 1024, 4096])
+@pytest.mark.parametrize("KN", [(4096, 4096), (4096, 11008), (11008, 4096)])
+def test_llama7b_projection_shapes_across_the_kernel_regimes(KN, M):
+    """configs[1] at its large-M points: the three LLaMA-7B projection shapes at M = 64 and 256 (stream-K
+    tcgen05 kernel), 1024 and 4096 (large-tile tcgen05 kernels; K = 11008 walks 172 k-blocks, so every
+    shared-memory ring wraps dozens of times).  Sampled rows - every 256-token tile of the output is hit -
+    against the fp64 dequantize-then-matmul on the CPU, and ALL elements against an fp32 matmul of the same
+    dequantized weights run by torch on the GPU (a consistency check of the rows the CPU did not sample)."""
+    K, N = KN
+    gen = torch.Generator().manual_seed(K + N + M)
+    q = torch.randint(-128, 128, (K, N), generator=gen, dtype=torch.int8)
+    s = (torch.rand(N, generator=gen) * 3e-4 + 1e-4).half()
+    x = torch.randn(M, K, generator=gen).half()
+    y = _run(x, q, s)
+    rows = sorted({r for t in range(0, M, 256) for r in (t, t + 127, t + 255) if r < M} | {1, M - 2, M - 1})
+    rows = torch.tensor(rows[:: max(1, len(rows) // 24)] + [M - 1])
+    ref = ops.gemm_w8a16_fp32(x[rows], q, s)
+    tol = 1e-2 * ref.abs().amax(1, keepdim=True)
+    assert ((y[rows].double() - ref).abs() <= tol).all()
+    w = (q.cuda().float() * s.cuda().float()[None])
+    full = x.cuda().float() @ w                       # fp32 (TF32 is off by default for matmul): checker only
+    err = (y.cuda().float() - full).abs()
+    assert bool((err <= 1e-2 * full.abs().amax(1, keepdim=True)).all()), float(err.max())
+    res = torch.randn(M, N, generator=gen).half()
+    yr = _run(x, q, s, residual=res)
+    assert torch.allclose(yr[rows].float(), ops.add_residual(y[rows], res[rows]).float(), rtol=2e-3, atol=2e-3)

@@ -101,3 +101,24 @@ def test_fp16_weight_shards_are_plain_slices():
     assert torch.equal(rows, w[1:3]) and rows.is_contiguous()
     same, _ = modeling._shard_cols(w, modeling._EMPTY, None, 0, 4, 3)
     assert same is w
+
+
+def test_graph_mode_decode_step_refuses_to_run_past_the_cache():
+    """With use_cuda_graph the step advances on the device, out of sight of the eager path's check
+    ("Exceed the maximum step length", LlamaMmha::forward_inc): decode_step must raise on the host before
+    anything is launched - here there is no GPU at all, so a launch would fail differently."""
+    import types
+    from eet_b200 import modeling
+    lm = modeling.EETLlamaForCausalLM.__new__(modeling.EETLlamaForCausalLM)
+    attn = types.SimpleNamespace(step_=16)
+    lm.model = types.SimpleNamespace(desc=types.SimpleNamespace(device=torch.device("cpu"), tp=None),
+                                     reorder_state=torch.empty(0).long(), layers=[types.SimpleNamespace(attention=attn)],
+                                     max_full_seq_len=16, past_kv_length=16)
+    lm.use_cuda_graph, lm._graph = True, None
+    with pytest.raises(RuntimeError, match="Exceed the maximum step length"):
+        lm.decode_step(torch.zeros(2, 1, dtype=torch.long))
+    assert attn.step_ == 16
+
+
+def test_device_status_codes_are_named():
+    assert set(EET._STATUS_TEXT) == {1, 2, 3, 4, 5, 6}

@@ -1,0 +1,96 @@
+"""Whole-model parity at the widths the benchmark quotes: two decoder layers of the LLaMA-7B architecture
+(hidden 4096, 32 heads, FFN 11008) at batch 8 with a 512-token prompt, and of the Baichuan-13B architecture
+(hidden 5120, 40 heads, FFN 13696, ALiBi) at batch 32 with a 256-token prompt, against the CPU oracle:
+prefill logits, decode steps beyond the prompt through the plain op calls, through the deferred-epilogue
+chain that generation uses, and as a replayed CUDA graph.  These are the shapes at which the decode kernels
+run with their full geometry (attention clusters of several CTAs per head, stream-K ranges that cut tile
+rows between CTAs, tensor-core GEMM tiles with wrapped rings), which the toy widths of the other model
+tests do not reach.
+
+Tolerance: |err| <= 2e-2 + 2e-2 * |ref| on fp32 logits of O(1) magnitude, as in the small-model tests."""
+import pytest
+import torch
+
+from model_util import OracleLM, random_hf_state_dict, tiny_config
+
+pytestmark = pytest.mark.gpu
+
+
+def _close(got, want):
+    got = got.float().cpu()
+    err = (got - want).abs()
+    ok = err <= 2e-2 + 2e-2 * want.abs()
+    return bool(ok.all()), float(err.max())
+
+
+def _decode_logits(model, ids, deferred, mask=None):
+    from eet_b200 import EET
+    if not deferred:
+        return model(ids, first_pass=False, attention_mask=mask).logits
+    with EET.deferred_epilogue():
+        hidden = model.model(input_ids=ids, first_pass=False, attention_mask=mask)
+    return model.lm_head(hidden)
+
+
+@pytest.mark.parametrize("padded", [False, True])
+def test_llama7b_width_two_layers(padded):
+    from eet_b200 import _lib, modeling
+    cfg = tiny_config(layers=2, hidden=4096, heads=32, d_ff=11008, vocab=1024)
+    sd = random_hf_state_dict(cfg, seed=21)
+    B, S, NEW, T = 8, 512, 4, 520
+    eet_dict = modeling.convert_llama_weights({k: v.cuda() for k, v in sd.items()}, torch.int8)
+    model = modeling.EETLlamaForCausalLM.from_eet(eet_dict, cfg, B, S, T, torch.int8)
+    lm = OracleLM(sd, cfg, max_len=T, batch=B)
+    gen = torch.Generator().manual_seed(22)
+    ids = torch.randint(0, cfg.vocab_size, (B, S + NEW), generator=gen)
+    mask, pad = None, None
+    if padded:
+        pad = torch.tensor([0, 1, 31, 32, 33, 200, 448, 511])
+        mask = (torch.arange(S)[None, :] >= pad[:, None]).long()
+    cmask = None if mask is None else mask.cuda()
+    got = model(ids[:, :S].cuda(), first_pass=True, attention_mask=cmask).logits
+    want = lm(ids[:, :S], True, pad)
+    for b in range(B):   # rows inside the padding carry no meaning
+        lo = 0 if pad is None else int(pad[b])
+        ok, err = _close(got[b, lo:], want[b, lo:])
+        assert ok, f"prefill, sequence {b}: max err {err}"
+    for i, t in enumerate(range(S, S + NEW)):
+        out = _decode_logits(model, ids[:, t:t + 1].cuda(), deferred=(i >= 2), mask=cmask)
+        ok, err = _close(out, lm(ids[:, t:t + 1], False, pad))
+        assert ok, f"decode step {t} (deferred={i >= 2}): max err {err}"
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0
+    if padded:
+        return
+    # the same steps as a CUDA graph: greedy tokens of generate() against the oracle's wherever its top-2
+    # margin is clear of the tolerance
+    model.use_cuda_graph = True
+    toks = model.generate(ids[:, :S].cuda(), NEW + 2).cpu()
+    logits = lm(ids[:, :S], True)[:, -1]
+    for t in range(NEW + 2):
+        top2 = logits.topk(2, -1).values
+        clear = (top2[:, 0] - top2[:, 1]) > 4e-2 + 4e-2 * top2[:, 0].abs()
+        tok = toks[:, S + t]
+        assert torch.equal(tok[clear], logits.argmax(-1)[clear]), f"generated token {t}"
+        logits = lm(tok.view(B, 1), False)[:, -1]
+    assert _lib.device_status() == 0
+
+
+def test_baichuan13b_width_two_layers_alibi():
+    from eet_b200 import _lib, modeling
+    cfg = tiny_config(layers=2, hidden=5120, heads=40, d_ff=13696, vocab=1024)   # != 32 layers -> ALiBi op
+    sd = random_hf_state_dict(cfg, seed=23, fused_qkv=True)
+    B, S, NEW, T = 32, 256, 4, 264
+    eet_dict = modeling.convert_baichuan_weights({k: v.cuda() for k, v in sd.items()}, torch.int8)
+    model = modeling.EETBaichuanForCausalLM.from_eet(eet_dict, cfg, B, S, T, torch.int8)
+    lm = OracleLM(sd, cfg, max_len=T, batch=B, rope=False, fused_qkv=True)
+    gen = torch.Generator().manual_seed(24)
+    ids = torch.randint(0, cfg.vocab_size, (B, S + NEW), generator=gen)
+    ok, err = _close(model(ids[:, :S].cuda(), first_pass=True).logits, lm(ids[:, :S], True))
+    assert ok, f"prefill: max err {err}"
+    for i, t in enumerate(range(S, S + NEW)):
+        out = _decode_logits(model, ids[:, t:t + 1].cuda(), deferred=(i >= 2))
+        ok, err = _close(out, lm(ids[:, t:t + 1], False))
+        assert ok, f"decode step {t} (deferred={i >= 2}): max err {err}"
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0

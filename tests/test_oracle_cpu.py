@@ -1,6 +1,7 @@
 """The oracle against its pins: golden vectors generated from the reference, and (where the library
 built from the reference checkout is present) the reference itself."""
 import glob
+import math
 import json
 import os
 
@@ -131,3 +132,72 @@ def test_convert_name_matches_reference(golden_dir):
     for model, table in names.items():
         for src, dst in table.items():
             assert convert_name(src, model) == dst
+
+
+# ---------------------------------------------------------------------------------------------------
+# The attention restatements against an independent formulation.  oracle/ops.py is written from the
+# reference's CUDA sources and nothing in the reference can run here to pin it; torch's
+# scaled_dot_product_attention (fp32, additive mask) shares no code with it.  What this pins: the masking
+# conventions (causal, left padding, which positions the ALiBi bias multiplies), the 1/sqrt(D) scale, the
+# softmax and the P.V contraction.  What it cannot pin: the reference's rounding points (fp16 logits, fp16
+# probabilities, the +1e-6 in the denominator), which only move the result inside the tolerance below.
+# ---------------------------------------------------------------------------------------------------
+def _sdpa(q, k, v, mask_add):
+    import torch.nn.functional as F
+    D = q.shape[-1]
+    return F.scaled_dot_product_attention(q.float(), k.float(), v.float(), attn_mask=mask_add, scale=1.0 / math.sqrt(D))
+
+
+@pytest.mark.parametrize("use_alibi", [False, True])
+def test_prefill_attention_matches_sdpa_with_padding_and_alibi(use_alibi):
+    from oracle import ops
+    gen = torch.Generator().manual_seed(11)
+    B, H, S, D = 3, 4, 37, 128
+    q, k, v = (torch.randn(B, H, S, D, generator=gen).half() for _ in range(3))
+    i = torch.arange(S)[:, None]
+    j = torch.arange(S)[None, :]
+    neg = torch.tensor(float("-inf"))
+    if use_alibi:
+        alibi = ops.alibi_mask(H, S).half()
+        got = ops.prefill_attention(q, k, v, None, alibi)
+        slopes = torch.tensor(ops.alibi_slopes(H))
+        mask = torch.where(j <= i, slopes[:, None, None] * j.float()[None], neg)[None]      # [1, H, S, S]
+        want = _sdpa(q, k, v, mask.expand(B, H, S, S))
+        rows = torch.ones(B, S, dtype=torch.bool)
+    else:
+        pad = torch.tensor([0, 5, 36])
+        got = ops.prefill_attention(q, k, v, pad, None)
+        ok = (j <= i)[None] & (j[None] >= pad.view(B, 1, 1))                                   # [B, S, S]
+        rows = torch.arange(S)[None, :] >= pad[:, None]                                        # rows with any key
+        mask = torch.where(ok, torch.tensor(0.0), neg)[:, None].expand(B, H, S, S).clone()
+        mask[~rows[:, None, :, None].expand(B, H, S, S)] = 0.0                                 # keep SDPA finite there
+        want = _sdpa(q, k, v, mask)
+        # rows above the left padding are zeroed by the reference (gpt2_self_softmax.cu:24-30)
+        assert (got[~rows[:, None, :].expand(B, H, S)] == 0).all()
+    sel = rows[:, None, :].expand(B, H, S)
+    err = (got.float() - want)[sel].abs()
+    assert float(err.max()) <= 4e-3 + 1e-2 * float(want[sel].abs().max()), float(err.max())
+
+
+@pytest.mark.parametrize("use_alibi", [False, True])
+def test_decode_attention_matches_sdpa_with_padding_and_alibi(use_alibi):
+    from oracle import ops
+    gen = torch.Generator().manual_seed(12)
+    B, H, D, T, step = 3, 4, 128, 48, 41
+    kc = torch.randn(B, H, T, D, generator=gen).half()
+    vc = torch.randn(B, H, T, D, generator=gen).half()
+    q, kn, vn = (torch.randn(B, H, D, generator=gen).half() for _ in range(3))
+    pad = None if use_alibi else torch.tensor([0, 7, 40])
+    alibi = ops.alibi_mask(H, T).half()[:, step - 1, :step] if use_alibi else None
+    got = ops.decode_attention(q, kn, vn, kc, vc, step, pad, alibi)
+    assert torch.equal(kc[:, :, step - 1], kn) and torch.equal(vc[:, :, step - 1], vn)        # appended in place
+    t = torch.arange(step)
+    if use_alibi:
+        slopes = torch.tensor(ops.alibi_slopes(H))
+        mask = (slopes[:, None] * t.float()[None])[None, :, None, :].expand(B, H, 1, step)
+    else:
+        mask = torch.where(t[None] >= pad[:, None], torch.tensor(0.0), torch.tensor(float("-inf")))
+        mask = mask[:, None, None, :].expand(B, H, 1, step)
+    want = _sdpa(q[:, :, None], kc[:, :, :step], vc[:, :, :step], mask)[:, :, 0]
+    err = (got.float() - want).abs()
+    assert float(err.max()) <= 4e-3 + 1e-2 * float(want.abs().max()), float(err.max())
