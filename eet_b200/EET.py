@@ -117,7 +117,6 @@ _STATUS_TEXT = {
     3: "decode attention: a pipeline wait ran out",
     4: "tensor-parallel exchange: a peer's partial sums never arrived",
     5: "decode attention: the step ran past the end of the KV cache",
-    6: "layer-chain kernel: a grid-wide barrier ran out",
 }
 
 

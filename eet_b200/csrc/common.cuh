@@ -37,17 +37,16 @@ void set_error(const char* fmt, ...);
 
 // Device-side status word.  A kernel that had to give up stores a non-zero code here and returns normally (uniform
 // control flow, tensor memory freed, nothing left in flight); the host reads and clears it with eet_device_status().
-//   1  decode GEMM (gemm_skinny / layer-chain kernel): a shared-memory pipeline wait ran out
+//   1  decode GEMM (gemm_skinny): a shared-memory pipeline wait ran out
 //   2  tensor-core GEMMs (gemm_mid, gemm_tc): a pipeline or tensor-memory wait ran out
 //   3  decode attention: a pipeline wait ran out
 //   4  tensor-parallel exchange: a peer's partial sums never arrived in this rank's inbox
 //   5  decode attention: the device-resident step was outside [1, cache length]; nothing was appended
-//   6  layer-chain kernel: the grid-wide barrier between two phases ran out
 // After a non-zero status the contents of every fp32 scratch buffer the failed kernel used are undefined.
 // (The library is built as one translation unit, so these definitions are seen exactly once.)
 #ifdef __CUDACC__
 __device__ int g_device_status = 0;
-// Polls allowed in the waits on OTHER CTAs or other GPUs (tensor-parallel inbox, grid barrier) before they give up;
+// Polls allowed in the waits on other GPUs (tensor-parallel inbox) before they give up;
 // eet_set_wait_limit() changes it.  The mbarrier waits inside one CTA use the compile-time kSpinLimit below.
 __device__ unsigned int g_wait_limit = 1u << 22;
 #endif

@@ -33,14 +33,13 @@ const char* eet_last_error(void);
  *   3  decode attention: a pipeline wait ran out
  *   4  tensor-parallel exchange: a peer's partial sums never arrived
  *   5  decode attention: the device-resident step was outside [1, T_max]; nothing was appended to the cache
- *   6  layer-chain kernel: a grid-wide barrier ran out
  * After a non-zero status the fp32 scratch buffers of the failed call hold undefined values: zero them (and, for
  * the tensor-parallel exchange, the inboxes and epoch counters of every rank) before the next call.
  * Synchronises the device.  The reference reports asynchronous failures the same way, at its next
  * check_cuda_error (csrc/op/common.hpp:55-64). */
 int eet_device_status(int* status_out);
 
-/* Number of polls after which a wait on another CTA or another GPU (tensor-parallel inbox, grid barrier) gives up
+/* Number of polls after which a wait on another GPU (the tensor-parallel inbox) gives up
  * on the current device; the default, 1 << 22, is a second or more.  Takes effect for kernels launched after the
  * call; synchronises the device.  No counterpart in the reference (it has no such waits). */
 int eet_set_wait_limit(unsigned int polls);

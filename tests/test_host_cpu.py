@@ -121,4 +121,4 @@ def test_graph_mode_decode_step_refuses_to_run_past_the_cache():
 
 
 def test_device_status_codes_are_named():
-    assert set(EET._STATUS_TEXT) == {1, 2, 3, 4, 5, 6}
+    assert set(EET._STATUS_TEXT) == {1, 2, 3, 4, 5}
