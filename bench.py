@@ -44,6 +44,9 @@ CFG = dict(hidden_size=4096, num_attention_heads=32, num_hidden_layers=32, inter
            rms_norm_eps=1e-6, hidden_act="silu", pad_token_id=None)
 BATCH, PROMPT = 8, 512
 WORKLOAD, FAMILY = "llama7b_arch_int8_decode_b8_prompt512", "llama"
+# The lm_head runs through the W8A16 path as well, its vocabulary sharded over the tensor-parallel ranks
+# (--lm-head fp16 keeps the reference's replicated fp16 torch.nn.Linear instead).
+LM_HEAD_INT8 = True
 
 # The headline configuration above is what a run without --workload measures.  The two other model-level
 # configurations of the reference's latency scripts are selectable for additional lines:
@@ -164,7 +167,8 @@ def build_model(tp, device_index, t_max, layers=None, batch=None, prompt=None, k
     dev = torch.device("cuda", device_index)
     d = random_eet_dict(cfg, dev)
     cls = modeling.EETBaichuanForCausalLM if FAMILY == "baichuan" else modeling.EETLlamaForCausalLM
-    model = cls.from_eet(d, cfg, batch or BATCH, prompt or PROMPT, t_max, torch.int8, device_id=device_index, tp=tp)
+    model = cls.from_eet(d, cfg, batch or BATCH, prompt or PROMPT, t_max, torch.int8, device_id=device_index, tp=tp,
+                         lm_head_int8=LM_HEAD_INT8)
     return (model, cfg, d) if keep_dict else (model, cfg)
 
 
@@ -181,15 +185,15 @@ def rewind(model, step):
 
 def kernel_launches_per_step(n_layers, batch, world):
     """Launches of this library's kernels in one decode step (NCCL and torch kernels are not counted)."""
-    deferred_max = 16 if world > 1 else 64
-    if batch <= deferred_max:
+    head = 2 if LM_HEAD_INT8 else 1   # int8: lm_head GEMM + fused argmax; fp16: argmax (the GEMM is cuBLAS, not counted)
+    if batch <= 64:
         # per layer: rmsnorm(+finalize), qkv gemm, decode attention, out gemm, rmsnorm(+finalize), gate+up gemm,
-        # swiglu(+finalize), down gemm; per step: advance_steps, embedding gather, final rmsnorm(+finalize), argmax
-        return 8 * n_layers + 4
+        # swiglu(+finalize), down gemm; per step: advance_steps, embedding gather, final rmsnorm(+finalize), lm_head
+        return 8 * n_layers + 3 + head
     # larger batches: every projection is an accumulate + finalize pair, gate and up are separate launches
     # (and with tensor parallelism the residual is added by its own kernel after the NCCL all-reduce)
     per_layer = 14 + (2 if world > 1 else 0)
-    return per_layer * n_layers + 4
+    return per_layer * n_layers + 3 + head
 
 
 # ------------------------------------------------------------------------------------------------ GEMM timing
@@ -376,6 +380,7 @@ def profile_kernels():
 def bench_config(n_layers, world, cuda_graph, warmup, steps):
     """The `config` object of the JSON line: both arms print the same keys."""
     return {"workload": WORKLOAD, "layers": n_layers, "global_batch": BATCH, "seq_len": PROMPT,
+            "lm_head": "int8, vocabulary-sharded over the ranks" if LM_HEAD_INT8 else "fp16, replicated (torch.nn.Linear)",
             "cache_len_during_timing": [PROMPT + warmup + 1, PROMPT + warmup + steps],
             "parallelism": f"tp{world}", "cuda_graph": cuda_graph,
             "l2": "weights (GBs per step) and KV cache exceed L2; no flush needed"}
@@ -436,11 +441,18 @@ def parity_check(tp, local, world, rank):
     H = cfg.num_attention_heads
     dec = ops.DecoderOracle(layers, H, cfg.hidden_size // H, cfg.rms_norm_eps, S + NEW + 2, BATCH,
                             rope=(FAMILY != "baichuan"))
-    emb, head, gamma = d["embed_tokens.weight"].cpu(), d["lm_head.weight"].cpu().float(), d["norm.weight"].cpu()
+    emb, gamma = d["embed_tokens.weight"].cpu(), d["norm.weight"].cpu()
+    if LM_HEAD_INT8:
+        hq, _, hs = EET.quant_weights(d["lm_head.weight"].t().contiguous(), torch.int8, True)
+        hq, hs = hq.cpu(), hs.cpu()
+    else:
+        head = d["lm_head.weight"].cpu().float()
 
     def oracle(tok, first):
-        x = ops.rmsnorm(dec.forward(emb[tok], first), gamma, cfg.rms_norm_eps)
-        return x[:, -1:].float() @ head.t()
+        x = ops.rmsnorm(dec.forward(emb[tok], first), gamma, cfg.rms_norm_eps)[:, -1]
+        if LM_HEAD_INT8:
+            return ops.gemm_w8a16(x, hq, hs).float().unsqueeze(1)
+        return (x.float() @ head.t()).unsqueeze(1)
 
     want = [oracle(ids[:, :S], True)] + [oracle(ids[:, t:t + 1], False) for t in range(S, S + NEW)]
     worst, worst_ratio = 0.0, 0.0
@@ -646,6 +658,9 @@ def main():
     ap.add_argument("--repeats", type=int, default=0,
                     help="repeats of the timed region (default: at least 5 and at least a second of load; "
                          "profiling runs pass 1)")
+    ap.add_argument("--lm-head", default="int8", choices=["int8", "fp16"],
+                    help="int8: lm_head through the W8A16 GEMM, vocabulary-sharded under tensor parallelism (default); "
+                         "fp16: the reference's replicated fp16 torch.nn.Linear")
     ap.add_argument("--no-parity", action="store_true", help="skip the 2-layer parity check against the CPU oracle")
     ap.add_argument("--profile-kernels", action="store_true",
                     help="run a few launches of the tensor-core kernels for a profiler capture and exit")
@@ -653,6 +668,8 @@ def main():
                     help="fill the KV cache with random data instead of running the prompt (profiling runs only)")
     args = ap.parse_args()
     select_workload(args.workload)
+    global LM_HEAD_INT8
+    LM_HEAD_INT8 = args.lm_head == "int8"
     if args.warmup < 3:
         args.warmup = 3
     if args.profile_kernels:

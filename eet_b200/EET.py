@@ -315,7 +315,7 @@ class _Pending:
 _pending = {}
 _defer = [False]
 _DECODE_MAX_M = 64       # below the tensor-core GEMM's first M
-_DECODE_MAX_M_TP = 16    # rows of the tensor-parallel peer buffers (tp.PeerBuffers.ROWS)
+_DECODE_MAX_M_TP = 64    # rows of the tensor-parallel peer buffers (tp.PeerBuffers.ROWS)
 
 
 def _defer_ok(M, desc):
@@ -327,7 +327,7 @@ def _defer_ok(M, desc):
 
 
 class deferred_epilogue:
-    """Context manager for a chain of decode-step ops of this module (M <= 64; 16 with tensor parallelism): inside
+    """Context manager for a chain of decode-step ops of this module (M <= 64): inside
     it an attention / FFN op returns its output tensor *before* the last GEMM's epilogue has run, and the next
     op (attention, FFN or LayerNorm of this module) completes it in its RMSNorm kernel.  Outputs still
     unfinished when the context ends are completed then, so callers outside never see stale memory."""

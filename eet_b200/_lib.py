@@ -41,6 +41,7 @@ SIGNATURES = {
     "eet_reorder_kv": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _sz, _vp]),
     "eet_advance_steps": (_i, [_vp, _i, _i, _vp]),
     "eet_argmax_rows": (_i, [_vp, _vp, _i, _i, _sz, _vp]),
+    "eet_lm_head_argmax": (_i, [_vp, _vp, _i, _i, _c.c_int64, _vp, _i, _i, _vp, _vp, _vp, _vp]),
     "eet_gather_rows": (_i, [_vp, _vp, _vp, _i, _i, _c.c_int64, _vp]),
 }
 

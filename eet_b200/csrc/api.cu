@@ -399,6 +399,15 @@ int eet_argmax_rows(const void* logits, int64_t* out, int rows, int n, size_t ro
     return launch_argmax_rows((const __half*)logits, out, rows, n, row_stride, (cudaStream_t)stream);
 }
 
+int eet_lm_head_argmax(float* sums, const void* scale, int M, int n_local, int64_t col_offset, void* const* peer_inbox,
+                       int world, int rank, int* epochs, int64_t* out_ids, void* logits_out, void* stream)
+{
+    EET_CHECK(M >= 0 && (M == 0 || (sums && scale && out_ids)), "eet_lm_head_argmax: NULL argument");
+    EET_CHECK(aligned16(sums) && aligned16(scale) && aligned16(logits_out), "eet_lm_head_argmax: pointers must be 16-byte aligned");
+    return launch_lm_head_argmax(sums, (const __half*)scale, M, n_local, (long long)col_offset, peer_inbox, world, rank, epochs,
+                                 out_ids, (__half*)logits_out, (cudaStream_t)stream);
+}
+
 int eet_gather_rows(const void* table, const int64_t* ids, void* out, int rows, int n, int64_t rows_in_table, void* stream)
 {
     EET_CHECK(rows >= 0 && n > 0 && rows_in_table > 0 && (rows == 0 || (table && ids && out)), "eet_gather_rows: bad arguments");

@@ -204,19 +204,22 @@ rmsnorm_finalize_kernel(float* __restrict__ sums, const __half* __restrict__ sca
 
 // Tensor-parallel form of rmsnorm_finalize_kernel: the all-reduce of a row-parallel projection fused into
 // the kernel that consumes it, with the latency of ONE NVLink hop.  Every rank's GEMM has left its partial
-// sums in local memory.  A row's CTA pushes them into an inbox in every peer's memory (peer stores over
-// NVLink) as 8-byte pairs {value bits, epoch}: a pair is written atomically, so the receiver needs no
-// separate flag and no fence - it polls its own (local) inbox until the pairs carry the epoch of this
-// exchange, the scheme of NCCL's low-latency protocol.  The partial rows are added in fp32 in rank order, so
-// every rank forms bit-identical sums; then scale, residual and RMSNorm as on one GPU.  Two inboxes
-// alternate (attention output projection / FFN down projection): a peer can overwrite an inbox only after
-// the exchange in between, which needs this rank's push, which follows this rank's reads.
+// sums in local memory.  A row's CTAs push them into an inbox in every peer's memory (peer stores over
+// NVLink) as 16-byte packets {v0, v1, v2, epoch}: the receiver needs no separate flag and no fence - it polls
+// its own (local) inbox until the packets carry the epoch of this exchange, the scheme of NCCL's low-latency
+// protocols.  ASSUMPTION: an aligned 16-byte vector store arrives in the peer's memory as one piece, i.e. a
+// 16-byte load never sees the new epoch word beside old value words (NVLink delivers such a store as one
+// packet; NCCL's 128-byte protocol rests on the same property).  The partial rows are added in fp32 in rank
+// order, so every rank forms bit-identical sums; then scale, residual and RMSNorm as on one GPU.  Two
+// inboxes alternate (attention output projection / FFN down projection): a peer can overwrite an inbox only
+// after the exchange in between, which needs this rank's push, which follows this rank's reads.
 struct TpPeers {
-    uint2* inbox[8];   // every rank's inbox [2][8 source ranks][16 rows][n] of {float bits, epoch} (index = rank)
+    uint4* inbox[8];   // every rank's inbox [2][8 source ranks][64 rows][n/8][3] packets (index = rank)
     int world, rank, which;
 };
 
-constexpr int kTpRows = 16;
+constexpr int kTpRows = 64;       // rows an inbox holds: decode batches up to 64
+constexpr int kTpPackets = 3;     // 16-byte packets per 8 values: {v0,v1,v2,e} {v3,v4,v5,e} {v6,v7,-,e}
 
 __device__ __forceinline__ uint4 ld_volatile_u4(const void* p)
 {
@@ -252,8 +255,12 @@ rmsnorm_finalize_tp_kernel(TpPeers peers, float* __restrict__ local_sums, int* _
     if (threadIdx.x == 0) s_epoch = epochs[peers.which * kTpRows + row] + 1;
     __syncthreads();
     const uint32_t epoch = (uint32_t)s_epoch;
-    const size_t slot_row = (size_t)(peers.which * 8) * kTpRows * n + (size_t)row * n;   // + src * kTpRows * n
     const int i = slice * blockDim.x + threadIdx.x;   // this thread's vector of 8 columns
+    const size_t row_packets = (size_t)(n >> 3) * kTpPackets;
+    // packet index of this thread's first packet inside the inbox of source rank `src`
+    auto slot = [&](int src) -> size_t {
+        return ((size_t)(peers.which * 8 + src) * kTpRows + row) * row_packets + (size_t)i * kTpPackets;
+    };
 
     // ---- push this rank's partial row to every peer, keep a copy, zero the local sums for the next GEMM ----
     float mine[8];
@@ -268,12 +275,10 @@ rmsnorm_finalize_tp_kernel(TpPeers peers, float* __restrict__ local_sums, int* _
 #pragma unroll
         for (int p = 0; p < 8; ++p) {
             if (p < peers.world && p != peers.rank) {
-                uint4* dst = reinterpret_cast<uint4*>(peers.inbox[p] + slot_row + (size_t)peers.rank * kTpRows * n +
-                                                      (size_t)i * 8);
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    dst[e] = make_uint4(__float_as_uint(mine[2 * e]), epoch, __float_as_uint(mine[2 * e + 1]), epoch);
-                }
+                uint4* dst = peers.inbox[p] + slot(peers.rank);
+                dst[0] = make_uint4(__float_as_uint(mine[0]), __float_as_uint(mine[1]), __float_as_uint(mine[2]), epoch);
+                dst[1] = make_uint4(__float_as_uint(mine[3]), __float_as_uint(mine[4]), __float_as_uint(mine[5]), epoch);
+                dst[2] = make_uint4(__float_as_uint(mine[6]), __float_as_uint(mine[7]), 0u, epoch);
             }
         }
     }
@@ -290,27 +295,24 @@ rmsnorm_finalize_tp_kernel(TpPeers peers, float* __restrict__ local_sums, int* _
             for (int e = 0; e < 8; ++e) v[e] += mine[e];
             continue;
         }
-        const uint4* src = reinterpret_cast<const uint4*>(peers.inbox[peers.rank] + slot_row + (size_t)r * kTpRows * n +
-                                                          (size_t)i * 8);
-        uint4 c[4];
+        const uint4* src = peers.inbox[peers.rank] + slot(r);
+        uint4 c[kTpPackets];
         uint32_t spins = 0;
         while (true) {
 #pragma unroll
-            for (int e = 0; e < 4; ++e) c[e] = ld_volatile_u4(src + e);
+            for (int e = 0; e < kTpPackets; ++e) c[e] = ld_volatile_u4(src + e);
             bool ok = true;
 #pragma unroll
-            for (int e = 0; e < 4; ++e) ok = ok && c[e].y == epoch && c[e].w == epoch;
+            for (int e = 0; e < kTpPackets; ++e) ok = ok && c[e].w == epoch;
             if (ok) break;
             if (++spins > spin_limit) {
                 g_device_status = 4;   // a peer never arrived: give up, the host reads the status word
                 break;
             }
         }
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            v[2 * e] += __uint_as_float(c[e].x);
-            v[2 * e + 1] += __uint_as_float(c[e].z);
-        }
+        v[0] += __uint_as_float(c[0].x); v[1] += __uint_as_float(c[0].y); v[2] += __uint_as_float(c[0].z);
+        v[3] += __uint_as_float(c[1].x); v[4] += __uint_as_float(c[1].y); v[5] += __uint_as_float(c[1].z);
+        v[6] += __uint_as_float(c[2].x); v[7] += __uint_as_float(c[2].y);
     }
     uint4 h = reinterpret_cast<const uint4*>(residual + (size_t)row * n)[i];
     h = finalize8(v, sc, &h);
@@ -565,6 +567,106 @@ argmax_rows_kernel(const __half* __restrict__ logits, int64_t* __restrict__ out,
     }
 }
 
+// Greedy token choice straight from the lm_head GEMM's fp32 sums, optionally over a vocabulary that is sharded
+// across tensor-parallel ranks.  One CTA per row: logit = fp16(sum * scale) - the value the reference's fp16
+// lm_head (torch.nn.Linear, python/eet/transformers/modeling_llama.py:471) would have stored - then the index
+// of the largest logit, the smallest index on ties (torch.argmax, python/eet/pipelines/generation.py:1185-1190);
+// the sums go back to zero.  With world > 1 every rank holds the columns [col_offset, col_offset + n) of the
+// vocabulary: the row's {logit bits, global index, epoch} goes into every peer's inbox as one 16-byte packet
+// (peer stores over NVLink, same delivery assumption as the partial-sum exchange above), this rank polls its
+// own inbox (bounded, status 4) and takes the best of all ranks - every rank the same token.  Two inbox
+// halves alternate with the epoch's parity: a peer's next packet for the same half needs this rank's packet
+// of the step in between, which is sent after this rank has read.
+struct ArgmaxPeers {
+    uint4* inbox[8];   // every rank's inbox [2][8 source ranks][64 rows] packets (index = rank)
+    int world, rank;
+};
+
+__global__ void __launch_bounds__(256)
+lm_head_argmax_kernel(ArgmaxPeers peers, float* __restrict__ sums, const __half* __restrict__ scale, int n, long long col_offset,
+                      int* __restrict__ epochs, int64_t* __restrict__ out, __half* __restrict__ logits_out)
+{
+    __shared__ float s_val[8];
+    __shared__ int s_idx[8];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int row = blockIdx.x;
+    float* srow = sums + (size_t)row * n;
+    float best = -INFINITY;
+    int best_i = 0x7fffffff;
+    for (int i = threadIdx.x; i < (n >> 3); i += blockDim.x) {
+        float v[8];
+        load_sums8(srow + (size_t)i * 8, v);
+        const uint4 sc = __ldg(reinterpret_cast<const uint4*>(scale) + i);
+        const uint4 lg = finalize8(v, sc, nullptr);
+        if (logits_out != nullptr) reinterpret_cast<uint4*>(logits_out + (size_t)row * n)[i] = lg;
+        const __half* hv = reinterpret_cast<const __half*>(&lg);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const float f = __half2float(hv[e]);
+            if (f > best) {   // strictly greater: the first (smallest) index of a maximum stays
+                best = f;
+                best_i = i * 8 + e;
+            }
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+        if (ov > best || (ov == best && oi < best_i)) {
+            best = ov;
+            best_i = oi;
+        }
+    }
+    if ((threadIdx.x & 31) == 0) {
+        s_val[threadIdx.x >> 5] = best;
+        s_idx[threadIdx.x >> 5] = best_i;
+    }
+    __syncthreads();
+    if (threadIdx.x != 0) return;
+    for (int w = 1; w < (int)(blockDim.x >> 5); ++w) {
+        if (s_val[w] > best || (s_val[w] == best && s_idx[w] < best_i)) {
+            best = s_val[w];
+            best_i = s_idx[w];
+        }
+    }
+    // a row of NaNs chooses nothing: local index 0, value -inf (it loses against any real logit of a peer)
+    long long best_g = col_offset + (best_i == 0x7fffffff ? 0 : best_i);
+    if (peers.world > 1) {
+        const uint32_t epoch = (uint32_t)epochs[row] + 1u;
+        const size_t half = (size_t)(epoch & 1u) * 8 * kTpRows;
+        const uint4 mine = make_uint4(__float_as_uint(best), (uint32_t)best_g, epoch, 0u);
+        for (int p = 0; p < peers.world; ++p) {
+            if (p != peers.rank) peers.inbox[p][half + (size_t)peers.rank * kTpRows + row] = mine;
+        }
+        const uint32_t spin_limit = g_wait_limit;
+        for (int r = 0; r < peers.world; ++r) {
+            if (r == peers.rank) continue;
+            const uint4* src = peers.inbox[peers.rank] + half + (size_t)r * kTpRows + row;
+            uint4 c;
+            uint32_t spins = 0;
+            while (true) {
+                c = ld_volatile_u4(src);
+                if (c.z == epoch) break;
+                if (++spins > spin_limit) {
+                    g_device_status = 4;
+                    break;
+                }
+            }
+            if (c.z != epoch) continue;
+            const float ov = __uint_as_float(c.x);
+            const long long og = (long long)c.y;
+            if (ov > best || (ov == best && og < best_g)) {
+                best = ov;
+                best_g = og;
+            }
+        }
+        epochs[row] = (int)epoch;
+    }
+    out[row] = best_g;
+}
+
 // out[r] = table[ids[r]] for rows of n fp16 values (n a multiple of 8): the token-embedding lookup that the
 // reference leaves to torch.nn.Embedding (python/eet/transformers/modeling_llama.py:281-283).
 __global__ void __launch_bounds__(256)
@@ -635,12 +737,13 @@ int launch_rmsnorm_finalize_tp(float* local_sums, void* const* peer_inbox, int w
     EET_CHECK(world >= 1 && world <= 8 && rank >= 0 && rank < world, "tensor-parallel rmsnorm: bad world %d / rank %d",
               world, rank);
     EET_CHECK(which == 0 || which == 1, "tensor-parallel rmsnorm: inbox index %d must be 0 or 1", which);
-    EET_CHECK(M <= kTpRows, "tensor-parallel rmsnorm: at most 16 rows (decode regime), got %d", M);
+    EET_CHECK(M <= kTpRows, "tensor-parallel rmsnorm: at most 64 rows (decode regime), got %d", M);
     if (M == 0) return 0;
     TpPeers peers = {};
     for (int r = 0; r < world; ++r) {
         EET_CHECK(peer_inbox[r] != nullptr, "tensor-parallel rmsnorm: NULL peer pointer");
-        peers.inbox[r] = reinterpret_cast<uint2*>(peer_inbox[r]);
+        EET_CHECK((reinterpret_cast<uintptr_t>(peer_inbox[r]) & 15u) == 0, "tensor-parallel rmsnorm: inboxes must be 16-byte aligned");
+        peers.inbox[r] = reinterpret_cast<uint4*>(peer_inbox[r]);
     }
     peers.world = world;
     peers.rank = rank;
@@ -738,6 +841,30 @@ int launch_argmax_rows(const __half* logits, int64_t* out, int rows, int n, size
     if (rows == 0) return 0;
     const int vec_ok = (reinterpret_cast<uintptr_t>(logits) % 16 == 0 && row_stride % 8 == 0) ? 1 : 0;
     EET_CUDA(launch_pdl(argmax_rows_kernel, dim3(rows), dim3(256), 0, stream, logits, out, n, row_stride, vec_ok));
+    return 0;
+}
+
+int launch_lm_head_argmax(float* sums, const __half* scale, int M, int n, long long col_offset, void* const* peer_inbox,
+                          int world, int rank, int* epochs, int64_t* out, __half* logits_out, cudaStream_t stream)
+{
+    EET_CHECK(n > 0 && n % 8 == 0, "lm_head argmax: the local vocabulary size %d must be a multiple of 8", n);
+    EET_CHECK(world >= 1 && world <= 8 && rank >= 0 && rank < world, "lm_head argmax: bad world %d / rank %d", world, rank);
+    EET_CHECK(col_offset >= 0 && col_offset + n <= 0x7fffffffLL, "lm_head argmax: vocabulary range out of bounds");
+    ArgmaxPeers peers = {};
+    peers.world = world;
+    peers.rank = rank;
+    if (world > 1) {
+        EET_CHECK(M <= kTpRows, "lm_head argmax: at most 64 rows with a sharded vocabulary, got %d", M);
+        EET_CHECK(peer_inbox != nullptr && epochs != nullptr, "lm_head argmax: a sharded vocabulary needs inboxes and epochs");
+        for (int r = 0; r < world; ++r) {
+            EET_CHECK(peer_inbox[r] != nullptr && (reinterpret_cast<uintptr_t>(peer_inbox[r]) & 15u) == 0,
+                      "lm_head argmax: inboxes must be non-NULL and 16-byte aligned");
+            peers.inbox[r] = reinterpret_cast<uint4*>(peer_inbox[r]);
+        }
+    }
+    if (M == 0) return 0;
+    EET_CUDA(launch_pdl(lm_head_argmax_kernel, dim3(M), dim3(256), 0, stream, peers, sums, scale, n, col_offset, epochs,
+                        out, logits_out));
     return 0;
 }
 

@@ -61,6 +61,8 @@ int launch_reorder_kv(__half* kcache, __half* vcache, const int64_t* index, int 
                       __half* ws, cudaStream_t stream);
 int launch_advance_steps(int* steps, int count, int delta, cudaStream_t stream);
 int launch_argmax_rows(const __half* logits, int64_t* out, int rows, int n, size_t row_stride, cudaStream_t stream);
+int launch_lm_head_argmax(float* sums, const __half* scale, int M, int n, long long col_offset, void* const* peer_inbox,
+                          int world, int rank, int* epochs, int64_t* out, __half* logits_out, cudaStream_t stream);
 int launch_gather_rows(const __half* table, const int64_t* ids, __half* out, int rows, int n, int64_t rows_in_table,
                        cudaStream_t stream);
 

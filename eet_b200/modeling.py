@@ -326,9 +326,89 @@ class EETBaichuanModel(_ModelBase):
         return mask.contiguous()
 
 
+class _LmHead:
+    """The lm_head of a causal LM.  By default the reference's: an fp16 torch.nn.Linear, replicated on every rank
+    (modeling_llama.py:370-372, called at :471).  With int8=True (not in the reference) the weight is quantized
+    like every other projection and runs through this library's W8A16 GEMM, and under tensor parallelism each rank
+    keeps only its vocabulary columns (whole 64-column tiles, tp.vocab_range): a decode step then reads 1/size of
+    half the bytes, and the greedy token is chosen from the GEMM's fp32 sums by one kernel that also settles the
+    choice between the ranks (eet_lm_head_argmax)."""
+
+    def __init__(self, weight_vh, device, int8, tp, max_rows):
+        self.vocab, self.hidden = weight_vh.shape
+        self.device, self.int8, self.max_rows = torch.device(device), bool(int8), int(max_rows)
+        self.tp = tp if (tp is not None and tp.size > 1 and int8) else None
+        self.lo, self.hi = 0, self.vocab
+        if not self.int8:
+            self.linear = nn.Linear(self.hidden, self.vocab, bias=False)
+            self.linear.load_state_dict({"weight": weight_vh})
+            self.linear = self.linear.half().to(self.device)
+            return
+        if self.tp is not None:
+            self.lo, self.hi = tp_mod.vocab_range(self.vocab, self.tp.rank, self.tp.size)
+        self.w, self.s = self._quantize(weight_vh)
+
+    def _quantize(self, weight_vh):
+        w = weight_vh.to(self.device).half().t().contiguous()       # [K = hidden, N = vocab]
+        packed, scale = quant_and_preprocess_weights(w, torch.int8, False)
+        return _shard_cols(packed, scale.half(), self.tp, self.lo, self.hi)
+
+    @property
+    def weight(self):
+        return self.linear.weight if not self.int8 else self.w
+
+    def load(self, weight_vh):
+        """New weights into the tensors a captured graph already points at."""
+        if not self.int8:
+            self.linear.weight.copy_(weight_vh.to(self.linear.weight))
+            return
+        w, s = self._quantize(weight_vh)
+        self.w.copy_(w)
+        self.s.copy_(s)
+
+    def __call__(self, hidden):
+        """Logits [..., vocab] (fp16) for hidden [..., hidden]; a sharded head gathers the ranks' columns."""
+        if not self.int8:
+            return self.linear(hidden)
+        x2d = hidden.reshape(-1, self.hidden)
+        local = EET.gemm_w8a16(x2d.contiguous(), self.w, self.s)
+        if self.tp is not None:
+            import torch.distributed as dist
+            ranges = [tp_mod.vocab_range(self.vocab, r, self.tp.size) for r in range(self.tp.size)]
+            width = max(hi - lo for lo, hi in ranges)
+            padded = torch.zeros((local.shape[0], width), dtype=local.dtype, device=local.device)
+            padded[:, : local.shape[1]] = local
+            parts = [torch.empty_like(padded) for _ in ranges]
+            dist.all_gather(parts, padded, group=self.tp.group)
+            local = torch.cat([p[:, : hi - lo] for p, (lo, hi) in zip(parts, ranges)], 1)
+        return local.view(*hidden.shape[:-1], self.vocab)
+
+    def greedy(self, hidden2d):
+        """Next token ids [B, 1] (int64) for hidden2d [B, hidden]: argmax of the fp16 logits, the smallest index on
+        ties, identical on every rank."""
+        B = hidden2d.shape[0]
+        hidden2d = hidden2d.contiguous()
+        world = 1 if self.tp is None else self.tp.size
+        if not self.int8 or B > self.max_rows or (world > 1 and B > tp_mod.PeerBuffers.ROWS):
+            return EET.argmax_rows(self(hidden2d)).view(-1, 1)
+        n = self.hi - self.lo
+        sums = EET._pool.zeros("lm_head_sums", self.max_rows * n, torch.float32, self.device)[: B * n].view(B, n)
+        out = EET._pool.get("lm_head_ids", self.max_rows, torch.int64, self.device)[:B]
+        EET.gemm_w8a16_accum(hidden2d, self.w, sums)
+        inbox = epochs = None
+        rank = 0
+        if world > 1:
+            pb = self.tp.peer_buffers(self.hidden, self.device)
+            inbox, epochs, rank = pb.argmax_ptrs, pb.argmax_epochs.data_ptr(), self.tp.rank
+        check(lib.eet_lm_head_argmax(sums.data_ptr(), self.s.data_ptr(), B, n, self.lo, inbox, world, rank, epochs,
+                                     out.data_ptr(), None, torch.cuda.current_stream().cuda_stream))
+        return out.view(B, 1)
+
+
 class _CausalLMBase:
-    """EETLlamaForCausalLM / EETBaichuanForCausalLM (modeling_llama.py:441-579): model + fp16 lm_head
-    (torch), called as model(input_ids, first_pass=..., attention_mask=...) -> .logits."""
+    """EETLlamaForCausalLM / EETBaichuanForCausalLM (modeling_llama.py:441-579): model + lm_head (fp16 through
+    torch as in the reference, or int8 and vocabulary-sharded, see _LmHead), called as
+    model(input_ids, first_pass=..., attention_mask=...) -> .logits."""
 
     MODEL = EETLlamaModel
 
@@ -340,25 +420,25 @@ class _CausalLMBase:
 
     @classmethod
     def from_eet(cls, model_dict, config, max_batch, max_prompt_seq_len, max_full_seq_len, data_type=torch.int8,
-                 device_id=0, tp=None):
+                 device_id=0, tp=None, lm_head_int8=False):
+        """The reference's arguments (modeling_llama.py:525-546) plus `tp` and `lm_head_int8` (quantize the lm_head
+        as well and shard its vocabulary over the tensor-parallel group; the reference keeps it in fp16)."""
         torch.set_grad_enabled(False)
         body = {k: v for k, v in model_dict.items() if "lm_head" not in k}
         model = cls.MODEL.from_eet(body, config, max_batch, max_prompt_seq_len, max_full_seq_len, data_type,
                                    device_id=device_id, tp=tp)
-        lm_head = nn.Linear(config.hidden_size, config.vocab_size, bias=False)
-        lm_head.load_state_dict({"weight": model_dict["lm_head.weight"]})
-        lm_head = lm_head.half().to(f"cuda:{device_id}")
+        lm_head = _LmHead(model_dict["lm_head.weight"], f"cuda:{device_id}", lm_head_int8, tp, max_batch)
         return cls(config, model, lm_head)
 
     @classmethod
     def from_torch(cls, torch_model, max_batch, max_prompt_seq_len, max_full_seq_len, data_type=torch.int8,
-                   device_id=0, tp=None):
+                   device_id=0, tp=None, lm_head_int8=False):
         """Converts a HF causal LM held in memory (the directory branch of from_pretrained,
         modeling_llama.py:559-561, without the disk read)."""
         sd = {k: v.half() if v.is_floating_point() else v for k, v in torch_model.state_dict().items()}
         conv = convert_baichuan_weights if any("W_pack" in k for k in sd) else convert_llama_weights
         return cls.from_eet(conv(sd, data_type), torch_model.config, max_batch, max_prompt_seq_len, max_full_seq_len,
-                            data_type, device_id=device_id, tp=tp)
+                            data_type, device_id=device_id, tp=tp, lm_head_int8=lm_head_int8)
 
     def update(self, torch_model):
         """Takes new weights from a HF model of the same architecture (re-quantizing them when the model is
@@ -367,7 +447,7 @@ class _CausalLMBase:
         sd = {k: v.half() if v.is_floating_point() else v for k, v in torch_model.state_dict().items()}
         conv = convert_baichuan_weights if any("W_pack" in k for k in sd) else convert_llama_weights
         model_dict = conv(sd, data_type)
-        self.lm_head.weight.copy_(model_dict["lm_head.weight"].to(self.lm_head.weight))
+        self.lm_head.load(model_dict["lm_head.weight"])
         self.model.update({k: v for k, v in model_dict.items() if "lm_head" not in k})
 
     def __call__(self, input_ids, first_pass=True, position_ids=None, attention_mask=None, reorder_state=None,
@@ -393,7 +473,7 @@ class _CausalLMBase:
         # inside the kernel that consumes it
         with EET.deferred_epilogue():
             hidden = self.model(input_ids=ids, first_pass=False)
-        return EET.argmax_rows(self.lm_head(hidden)[:, -1, :]).view(-1, 1)
+        return self.lm_head.greedy(hidden[:, -1, :])
 
     def decode_logits(self, ids):
         """Logits [B, 1, vocab] of one decode step for ids [B, 1], computed by the same chain of kernels that
@@ -470,13 +550,15 @@ class _CausalLMBase:
         self.end_graph()
         if attention_mask is not None and self.use_cuda_graph:
             self.model.pre_padding_len = torch.sum(1 - attention_mask, 1, True).to(self.model.desc.device).long()
-        out = self(input_ids, first_pass=True, attention_mask=attention_mask)
-        nxt = torch.argmax(out.logits[:, -1, :], dim=-1, keepdim=True)
+        # only the last position's logits are needed to choose the first new token: the lm_head runs on that
+        # row alone (the reference computes and discards the logits of every prompt position, modeling_llama.py:471)
+        hidden = self.model(input_ids=input_ids, first_pass=True, attention_mask=attention_mask)
+        nxt = self.lm_head.greedy(hidden[:, -1, :].contiguous()).clone()
         toks = [input_ids, nxt]
         for _ in range(max_new_tokens - 1):
             if attention_mask is not None and not self.use_cuda_graph:
                 hidden = self.model(input_ids=nxt, first_pass=False, attention_mask=attention_mask)
-                nxt = torch.argmax(self.lm_head(hidden)[:, -1, :], dim=-1, keepdim=True)
+                nxt = self.lm_head.greedy(hidden[:, -1, :]).clone()
             else:
                 nxt = self.decode_step(nxt).clone()
             toks.append(nxt)

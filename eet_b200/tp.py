@@ -46,13 +46,15 @@ class TensorParallel:
 
 
 class PeerBuffers:
-    """What the fused tensor-parallel reduction needs on every rank: two local fp32 partial-sum buffers
-    [rows][hidden] (attention-output / FFN-down projections alternate between them), and an inbox
-    [2][8 source ranks][rows][hidden] of {float bits, epoch} pairs that the OTHER ranks write into over NVLink.
+    """What the fused tensor-parallel exchanges need on every rank: two local fp32 partial-sum buffers
+    [rows][hidden] (attention-output / FFN-down projections alternate between them), an inbox
+    [2][8 source ranks][rows][hidden / 8][3] of 16-byte packets {value, value, value, epoch} that the OTHER
+    ranks write into over NVLink (eet_rmsnorm_finalize_tp), and behind it a small inbox [2][8][rows] of
+    {logit, index, epoch} packets for the greedy token choice over a sharded vocabulary (eet_lm_head_argmax).
     The inboxes are shared through CUDA IPC handles exchanged over the process group.  Lets the decode path
-    replace `NCCL all-reduce -> RMSNorm` by one kernel (eet_rmsnorm_finalize_tp)."""
+    replace `NCCL all-reduce -> RMSNorm` by one kernel."""
 
-    ROWS = 16
+    ROWS = 64
 
     def __init__(self, tp, hidden, device):
         import ctypes
@@ -63,8 +65,11 @@ class PeerBuffers:
         self.tp, self.hidden = tp, hidden
         n = self.ROWS * hidden
         self.local_sums = torch.zeros(2 * n, dtype=torch.float32, device=device)
-        self.local_inbox = torch.zeros(2 * 8 * n * 2, dtype=torch.int32, device=device)   # 8-byte pairs
+        sum_words = 2 * 8 * self.ROWS * (hidden // 8) * 3 * 4        # 16-byte packets, 3 per 8 values
+        argmax_words = 2 * 8 * self.ROWS * 4                         # one 16-byte packet per (half, rank, row)
+        self.local_inbox = torch.zeros(sum_words + argmax_words, dtype=torch.int32, device=device)
         self.epochs = torch.zeros(2 * self.ROWS, dtype=torch.int32, device=device)
+        self.argmax_epochs = torch.zeros(self.ROWS, dtype=torch.int32, device=device)
         torch.cuda.synchronize(device)
         everyone = [None] * tp.size
         dist.all_gather_object(everyone, (reduce_tensor(self.local_inbox), device.index), group=tp.group)
@@ -91,12 +96,14 @@ class PeerBuffers:
         dist.barrier(group=tp.group)
         self._n = n
         self.inbox_ptrs = (ctypes.c_void_p * tp.size)(*[t.data_ptr() for t in self.inboxes])
+        self.argmax_ptrs = (ctypes.c_void_p * tp.size)(*[t.data_ptr() + 4 * sum_words for t in self.inboxes])
 
     def clear_local(self):
         """Zeroes this rank's partial sums, inbox and epoch counters (see TensorParallel.reset_peer_buffers)."""
         self.local_sums.zero_()
         self.local_inbox.zero_()
         self.epochs.zero_()
+        self.argmax_epochs.zero_()
 
     def buffer(self, which, rows):
         """This rank's partial-sum buffer 0 (attention output projection) or 1 (FFN down projection)."""
@@ -141,6 +148,17 @@ def ff_range(d_ff, rank, size):
     if units < size:
         raise ValueError(f"d_ff {d_ff} has fewer 64-channel tiles than the {size} ranks")
     return unit * (units * rank // size), unit * (units * (rank + 1) // size)
+
+
+def vocab_range(vocab, rank, size):
+    """Vocabulary columns [lo, hi) of the lm_head owned by `rank`: whole 64-column tiles of the packed weight,
+    unevenly when the tiles do not divide (32000 = 500 tiles over 8 ranks gives 62 or 63 tiles per rank)."""
+    if vocab % 64:
+        raise ValueError(f"vocabulary size {vocab} must be a multiple of 64 for an int8 lm_head")
+    tiles = vocab // 64
+    if tiles < size:
+        raise ValueError(f"vocabulary of {vocab} has fewer 64-column tiles than the {size} ranks")
+    return 64 * (tiles * rank // size), 64 * (tiles * (rank + 1) // size)
 
 
 def shard_plan(num_heads, d_ff, size):

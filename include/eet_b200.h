@@ -162,12 +162,13 @@ int eet_rmsnorm_finalize(float* sums, const void* scale, const void* residual, v
                          void* xn_out, int M, int n, float eps, void* stream);
 
 /*
- * Tensor-parallel form of eet_rmsnorm_finalize (decode, M <= 16): the all-reduce of a row-parallel projection
+ * Tensor-parallel form of eet_rmsnorm_finalize (decode, M <= 64): the all-reduce of a row-parallel projection
  * fused into the kernel that consumes it.  local_sums: this rank's partial sums [M][n] fp32 (zeroed by the call).
- * peer_inbox[r] (host array of `world` device pointers, r = rank): every rank's inbox, 2 * 8 * 16 * n pairs of
- * {float bits, int32 epoch} (8 bytes each, zero at start), in memory all ranks can reach (CUDA IPC / peer
- * access).  which: 0 or 1, the inbox of this exchange - consecutive exchanges must alternate.  epochs: 32 int32 of
- * this rank, zero at start.  Each row's CTA pushes its partial row into every peer's inbox, then polls its own
+ * peer_inbox[r] (host array of `world` device pointers, r = rank): every rank's inbox, 2 * 8 * 64 * (n / 8) * 3
+ * packets of 16 bytes {value, value, value, int32 epoch} (zero at start), in memory all ranks can reach (CUDA IPC /
+ * peer access); an aligned 16-byte store is assumed to arrive there as one piece.  which: 0 or 1, the inbox of this
+ * exchange - consecutive exchanges must alternate.  epochs: 128 int32 of this rank, zero at start.  Each row's CTAs
+ * push the partial row into every peer's inbox, then poll their own
  * inbox - a bounded wait, status 4 in eet_device_status if a peer never arrives - and adds the partial rows in
  * fp32 in rank order; then scale, residual, RMSNorm as eet_rmsnorm_finalize.  The reference is single-GPU: no
  * counterpart.
@@ -250,6 +251,22 @@ int eet_advance_steps(int* steps, int count, int delta, void* stream);
  * smallest index on ties: the greedy token choice.  The reference leaves it to torch.argmax
  * (python/eet/pipelines/generation.py:1185-1190). */
 int eet_argmax_rows(const void* logits, int64_t* out, int rows, int n, size_t row_stride, void* stream);
+
+/*
+ * Greedy token choice straight from the fp32 sums of an int8 lm_head projection (eet_gemm_w8a16_accum), for a
+ * vocabulary that may be sharded over tensor-parallel ranks: logit = fp16(sums * scale), out_ids[r] = global index
+ * of the largest logit of row r (the smallest index on ties); sums is zeroed.  This rank holds the vocabulary
+ * columns [col_offset, col_offset + n_local).  With world > 1 each row's {logit, index, epoch} is pushed into every
+ * peer's inbox as one 16-byte packet and the best of all ranks is taken, the same on every rank: peer_inbox[r] is
+ * rank r's inbox of 2 * 8 * 64 packets of 16 bytes (zero at start, reachable by every rank), epochs 64 int32 of
+ * this rank (zero at start), M <= 64; the wait for the peers is bounded (status 4).  With world == 1 peer_inbox and
+ * epochs may be NULL and M is not limited.  logits_out, if not NULL, receives the fp16 logits [M][n_local].
+ * Replaces: the fp16 lm_head + torch.argmax of the reference's generation loop
+ *           (python/eet/transformers/modeling_llama.py:471, python/eet/pipelines/generation.py:1185-1190); the
+ *           int8 weights and the sharding have no counterpart there.
+ */
+int eet_lm_head_argmax(float* sums, const void* scale, int M, int n_local, int64_t col_offset, void* const* peer_inbox,
+                       int world, int rank, int* epochs, int64_t* out_ids, void* logits_out, void* stream);
 
 /* out[r][0..n) = table[ids[r]][0..n), fp16, n a multiple of 8, ids device int64 (an id outside
  * [0, rows_in_table) reads row 0): the token-embedding lookup, torch.nn.Embedding in the reference

@@ -67,8 +67,11 @@ class OracleLM:
     """Embedding -> DecoderOracle -> final RMSNorm -> lm_head, all on the CPU, mirroring
     EETLlamaForCausalLM.__call__ (python/eet/transformers/modeling_llama.py:262-297,452-491)."""
 
-    def __init__(self, sd, cfg, max_len, batch, rope=True, fused_qkv=False, exact=True, int8=True):
+    def __init__(self, sd, cfg, max_len, batch, rope=True, fused_qkv=False, exact=True, int8=True, lm_head_int8=False):
         self.sd, self.cfg = sd, cfg
+        # with lm_head_int8 the head is quantized like the layer projections (an option of the library that the
+        # reference does not have) and the logits are rounded to fp16 as a GEMM epilogue would round them
+        self.head = _quant(sd["lm_head.weight"]) if lm_head_int8 else None
         self.dec = ops.DecoderOracle(oracle_layers(sd, cfg, fused_qkv, int8), cfg.num_attention_heads,
                                      cfg.hidden_size // cfg.num_attention_heads, cfg.rms_norm_eps, max_len, batch,
                                      rope=rope, exact=exact)
@@ -79,6 +82,9 @@ class OracleLM:
         x = self.sd["model.embed_tokens.weight"][ids]
         x = self.dec.forward(x, first_pass, pad_len)
         x = ops.rmsnorm(x, self.sd["model.norm.weight"], self.cfg.rms_norm_eps)
+        if self.head is not None:
+            B, S, h = x.shape
+            return ops.gemm_w8a16(x.reshape(B * S, h), self.head[0], self.head[1]).float().view(B, S, -1)
         return (x.float() @ self.sd["lm_head.weight"].float().t())
 
 

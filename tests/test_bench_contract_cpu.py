@@ -60,9 +60,10 @@ def test_reference_arm_is_silent_on_other_ranks(monkeypatch, capsys):
 
 
 def test_launch_count_and_workloads():
-    assert bench.kernel_launches_per_step(32, 8, 1) == 8 * 32 + 4
-    assert bench.kernel_launches_per_step(32, 8, 4) == 8 * 32 + 4
-    assert bench.kernel_launches_per_step(40, 32, 1) == 8 * 40 + 4        # deferred chain up to 64 rows on one GPU
-    assert bench.kernel_launches_per_step(80, 64, 4) == 16 * 80 + 4       # tensor parallel above 16 rows
+    assert bench.kernel_launches_per_step(32, 8, 1) == 8 * 32 + 5         # int8 lm_head: GEMM + fused argmax
+    assert bench.kernel_launches_per_step(32, 8, 4) == 8 * 32 + 5
+    assert bench.kernel_launches_per_step(40, 32, 1) == 8 * 40 + 5        # deferred chain up to 64 rows
+    assert bench.kernel_launches_per_step(80, 64, 4) == 8 * 80 + 5        # ... with tensor parallelism too
+    assert bench.kernel_launches_per_step(80, 128, 4) == 16 * 80 + 5
     assert set(bench.WORKLOADS) == {"llama7b", "baichuan13b", "llama65b"}
     assert bench.WORKLOADS["llama7b"] is None and bench.BATCH == 8 and bench.PROMPT == 512

@@ -211,3 +211,52 @@ def test_decode_batch_above_16_uses_the_stream_k_kernel_and_matches_oracle():
     assert torch.equal(eager, graphed)
     from eet_b200 import _lib
     assert _lib.device_status() == 0
+
+
+def test_int8_lm_head_logits_and_greedy_choice():
+    """lm_head_int8=True (an option beyond the reference): the head is quantized like the other projections; its
+    logits against the oracle with the same quantized head, and the fused greedy kernel against argmax of them."""
+    from eet_b200 import modeling
+    cfg = tiny_config(vocab=320)
+    sd = random_hf_state_dict(cfg, seed=11)
+    B, S, T = 2, 6, 16
+    eet_dict = modeling.convert_llama_weights({k: v.clone() for k, v in sd.items()}, torch.int8)
+    model = modeling.EETLlamaForCausalLM.from_eet(eet_dict, cfg, B, 8, T, torch.int8, lm_head_int8=True)
+    assert model.lm_head.int8 and model.lm_head.w.dtype == torch.int8
+    lm = OracleLM(sd, cfg, max_len=T, batch=B, lm_head_int8=True)
+    gen = torch.Generator().manual_seed(12)
+    ids = torch.randint(0, cfg.vocab_size, (B, S + 3), generator=gen)
+    assert _logits_close(model(ids[:, :S].cuda(), first_pass=True).logits, lm(ids[:, :S], True))
+    for t in range(S, S + 3):
+        logits = model.decode_logits(ids[:, t:t + 1].cuda())
+        assert _logits_close(logits, lm(ids[:, t:t + 1], False))
+    # greedy: the fused kernel works on the fp32 sums and must agree with argmax over the fp16 logits
+    hidden = torch.randn(B, cfg.hidden_size, generator=gen).half().cuda()
+    want = model.lm_head(hidden).float().argmax(-1).view(B, 1)
+    assert torch.equal(model.lm_head.greedy(hidden), want)
+    eager = model.generate(ids[:, :S].cuda(), 5).cpu()
+    model.use_cuda_graph = True
+    assert torch.equal(model.generate(ids[:, :S].cuda(), 5).cpu(), eager)
+
+
+@pytest.mark.parametrize("M,n", [(1, 64), (5, 320), (8, 32000), (64, 4096)])
+def test_lm_head_argmax_kernel(M, n):
+    from eet_b200._lib import check, lib
+    gen = torch.Generator().manual_seed(M + n)
+    sums = (torch.randn(M, n, generator=gen) * 500).cuda()
+    scale = (torch.rand(n, generator=gen) * 1e-3 + 1e-4).half().cuda()
+    logits_ref = (sums * scale.float()[None]).half()
+    # plant exact ties at the maximum: the smallest index must win
+    top = logits_ref.float().amax(1)
+    for r in range(M):
+        j = int(torch.randint(0, n, (1,), generator=gen))
+        sums[r, j] = float(top[r]) / float(scale[j].float()) if float(scale[j]) > 0 else sums[r, j]
+    logits_ref = (sums * scale.float()[None]).half()
+    out = torch.full((M,), -1, dtype=torch.int64, device="cuda")
+    logits = torch.empty(M, n, dtype=torch.float16, device="cuda")
+    check(lib.eet_lm_head_argmax(sums.data_ptr(), scale.data_ptr(), M, n, 7 * 64, None, 1, 0, None, out.data_ptr(),
+                                 logits.data_ptr(), torch.cuda.current_stream().cuda_stream))
+    torch.cuda.synchronize()
+    assert torch.equal(logits, logits_ref)
+    assert torch.equal(out.cpu(), logits_ref.float().argmax(1).cpu() + 7 * 64)
+    assert float(sums.abs().max()) == 0

@@ -1,6 +1,7 @@
 """Tensor-parallel model on 2, 4 and 8 GPUs (one process per GPU, NCCL for the plumbing) against the CPU oracle,
 at the width the benchmark runs: two decoder layers of the LLaMA-7B architecture (hidden 4096, 32 heads, FFN
-11008 - 86 strips of 128 channels, so the FFN shards are uneven at 4 and 8 ranks), batch 8, a 64-token prompt
+11008 - 86 strips of 128 channels, so the FFN shards are uneven at 4 and 8 ranks; int8 lm_head with its
+vocabulary sharded over the ranks), batch 8, a 64-token prompt
 and decode steps through the plain op calls (NCCL all-reduce), through the deferred-epilogue chain (the fused
 exchange inside the RMSNorm head, with the cluster geometry and inbox addressing of the real hidden size) and
 as a replayed CUDA graph.  Rank 0 compares its logits with the oracle; all ranks must hold bit-identical
@@ -40,7 +41,11 @@ def _worker(rank, world, port, q, small):
         eet_dict = modeling.convert_llama_weights({k: v.to(dev) for k, v in sd.items()}, torch.int8)
         gen = torch.Generator().manual_seed(1)
         ids = torch.randint(0, cfg.vocab_size, (B, S + NEW), generator=gen)
-        model = modeling.EETLlamaForCausalLM.from_eet(eet_dict, cfg, B, S, T, torch.int8, device_id=rank, tp=tp)
+        # the full-width case also quantizes the lm_head and shards its 1024-entry vocabulary (16 tiles: even over
+        # 2, 4, 8 ranks); the small case keeps the reference's replicated fp16 head
+        head_int8 = not small
+        model = modeling.EETLlamaForCausalLM.from_eet(eet_dict, cfg, B, S, T, torch.int8, device_id=rank, tp=tp,
+                                                      lm_head_int8=head_int8)
         del eet_dict
         outs = [model(ids[:, :S].to(dev), first_pass=True).logits.float().cpu()]
         for i, t in enumerate(range(S, S + NEW)):
@@ -48,9 +53,7 @@ def _worker(rank, world, port, q, small):
             if i < 2:     # plain op calls: NCCL all-reduce + separate residual kernel
                 outs.append(model(step_ids, first_pass=False).logits.float().cpu())
             else:         # the chain generation uses: fused exchange in the next block's RMSNorm head
-                with EET.deferred_epilogue():
-                    hidden = model.model(input_ids=step_ids, first_pass=False)
-                outs.append(model.lm_head(hidden).float().cpu())
+                outs.append(model.decode_logits(step_ids).float().cpu())
         toks = model.generate(ids[:, :S].to(dev), NEW + 2).cpu()
         model.use_cuda_graph = True
         toks_g = model.generate(ids[:, :S].to(dev), NEW + 2).cpu()
@@ -64,7 +67,7 @@ def _worker(rank, world, port, q, small):
         verdict = [None]
         if rank == 0:
             try:
-                lm = OracleLM(sd, cfg, max_len=T, batch=B)
+                lm = OracleLM(sd, cfg, max_len=T, batch=B, lm_head_int8=head_int8)
                 want = [lm(ids[:, :S], True)] + [lm(ids[:, t:t + 1], False) for t in range(S, S + NEW)]
                 for i, (a, b) in enumerate(zip(outs, want)):
                     err = (a - b).abs()
@@ -72,7 +75,7 @@ def _worker(rank, world, port, q, small):
                 # greedy tokens (eager, then as a replayed CUDA graph) against the oracle's wherever its top-2
                 # margin is clear of the tolerance; the oracle follows the library's tokens (same history)
                 for name, seq in (("eager", toks), ("graph", toks_g)):
-                    lm2 = OracleLM(sd, cfg, max_len=T, batch=B)
+                    lm2 = OracleLM(sd, cfg, max_len=T, batch=B, lm_head_int8=head_int8)
                     logits = lm2(ids[:, :S], True)[:, -1]
                     for t in range(NEW + 2):
                         top2 = logits.topk(2, -1).values

@@ -24,14 +24,16 @@ def test_tensor_parallel_inbox_wait_runs_out_and_reports_status_4():
     M, n, world = 4, 4096, 2
     gen = torch.Generator().manual_seed(0)
     sums = torch.randn(M, n, generator=gen).cuda()
+    sums_before = sums.clone()
     scale = (torch.rand(n, generator=gen) * 1e-2).half().cuda()
     res = torch.randn(M, n, generator=gen).half().cuda()
     gamma = torch.ones(n).half().cuda()
     h_out = torch.empty(M, n, dtype=torch.float16, device="cuda")
     xn = torch.empty_like(h_out)
-    inbox = [torch.zeros(2 * 8 * 16 * n * 2, dtype=torch.int32, device="cuda") for _ in range(world)]
+    # an inbox: [2][8 source ranks][64 rows][n / 8][3] packets of 16 bytes {value, value, value, epoch}
+    inbox = [torch.zeros(2 * 8 * 64 * (n // 8) * 3 * 4, dtype=torch.int32, device="cuda") for _ in range(world)]
     ptrs = (ctypes.c_void_p * world)(*[t.data_ptr() for t in inbox])
-    epochs = torch.zeros(32, dtype=torch.int32, device="cuda")
+    epochs = torch.zeros(128, dtype=torch.int32, device="cuda")
     assert _lib.device_status() == 0
     check(lib.eet_set_wait_limit(2000))
     try:
@@ -43,8 +45,12 @@ def test_tensor_parallel_inbox_wait_runs_out_and_reports_status_4():
         assert _lib.device_status() == 0   # reading clears it
         # the kernel kept its bookkeeping consistent: sums consumed, epoch advanced, pairs pushed to the "peer"
         assert float(sums.abs().max()) == 0 and int(epochs[0]) == 1
-        pushed = inbox[1].view(2, 8, 16, n, 2)[0, 0, :M]           # inbox 0, source rank 0
-        assert bool((pushed[..., 1] == 1).all())
+        pushed = inbox[1].view(2, 8, 64, n // 8, 3, 4)[0, 0, :M]    # inbox 0, source rank 0
+        assert bool((pushed[..., 3] == 1).all())
+        # the packets carry the partial sums themselves: {v0, v1, v2}, {v3, v4, v5}, {v6, v7, -}
+        vals = pushed.view(torch.float32)
+        got = torch.cat([vals[..., 0, :3], vals[..., 1, :3], vals[..., 2, :2]], -1).reshape(M, n)
+        assert torch.equal(got, sums_before)
     finally:
         check(lib.eet_set_wait_limit(1 << 22))
     # an ordinary call afterwards is unaffected
@@ -111,3 +117,31 @@ def test_check_device_status_rezeroes_the_pooled_scratch():
     assert float(buf.abs().max()) == 0
     EET.check_device_status()   # clean again
     assert _lib.device_status() == 0
+
+
+def test_lm_head_argmax_peer_wait_runs_out_and_still_answers():
+    """eet_lm_head_argmax with a sharded vocabulary whose peer never sends its packet: the wait gives up (status
+    4) and the kernel still writes this rank's own best index."""
+    from eet_b200 import _lib
+    from eet_b200._lib import check, lib
+    M, n, world = 3, 512, 2
+    gen = torch.Generator().manual_seed(3)
+    sums = torch.randn(M, n, generator=gen).cuda()
+    scale = torch.full((n,), 0.01).half().cuda()
+    want = (sums.cpu() * scale.cpu().float()).half().float().argmax(1) + 1024   # of the fp16 logits, first on ties
+    inbox = [torch.zeros(2 * 8 * 64 * 4, dtype=torch.int32, device="cuda") for _ in range(world)]
+    ptrs = (ctypes.c_void_p * world)(*[t.data_ptr() for t in inbox])
+    epochs = torch.zeros(64, dtype=torch.int32, device="cuda")
+    out = torch.full((M,), -1, dtype=torch.int64, device="cuda")
+    check(lib.eet_set_wait_limit(2000))
+    try:
+        check(lib.eet_lm_head_argmax(sums.data_ptr(), scale.data_ptr(), M, n, 1024, ptrs, world, 0, epochs.data_ptr(),
+                                     out.data_ptr(), None, _stream()))
+        torch.cuda.synchronize()
+        assert _lib.device_status() == 4
+    finally:
+        check(lib.eet_set_wait_limit(1 << 22))
+    assert torch.equal(out.cpu(), want) and float(sums.abs().max()) == 0 and int(epochs[0]) == 1
+    # the packet for the peer went out: {logit bits, global index, epoch, -} in half 1 (epoch 1), source rank 0
+    sent = inbox[1].view(2, 8, 64, 4)[1, 0, :M].cpu()
+    assert torch.equal(sent[:, 1].long(), want) and bool((sent[:, 2] == 1).all())
