@@ -48,6 +48,7 @@ static inline bool aligned16(const void* p)
 #include "gemm_skinny.cu"
 #include "gemm_tc.cu"
 #include "gemm_mid.cu"
+#include "attention_tc.cu"
 #include "glue.cu"
 #include "noalloc.cu"
 #include "quantize.cu"
@@ -334,6 +335,13 @@ int eet_prefill_mha(const void* q, const void* kcache, const void* vcache, void*
     EET_CHECK(q && kcache && vcache && ctx && B >= 0 && S >= 0 && H > 0, "eet_prefill_mha: bad arguments");
     EET_CHECK(aligned16(q) && aligned16(kcache) && aligned16(vcache) && aligned16(ctx),
               "eet_prefill_mha: pointers must be 16-byte aligned");
+    // long prompts: tcgen05 kernel (128 x 128 tiles); short ones: the mma.sync kernel with 64 x 64 tiles
+    static const bool no_tc = getenv("EET_NO_PREFILL_TC") != nullptr;
+    if (!no_tc && prefill_mha_tc_supported(S, D) && B > 0) {
+        EET_CHECK(S <= T_max, "prefill attention: prompt length %d exceeds the cache length %d", S, T_max);
+        return launch_prefill_mha_tc((const __half*)q, (const __half*)kcache, (const __half*)vcache, (__half*)ctx, B, S, H,
+                                     T_max, pad_len, (const __half*)alibi, alibi_stride, (cudaStream_t)stream);
+    }
     return launch_prefill_mha((const __half*)q, (const __half*)kcache, (const __half*)vcache, (__half*)ctx, B, S, H, D,
                               T_max, pad_len, (const __half*)alibi, alibi_stride, (cudaStream_t)stream);
 }

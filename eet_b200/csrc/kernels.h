@@ -90,4 +90,10 @@ int launch_prefill_mha(const __half* q, const __half* kcache, const __half* vcac
                        int D, int T_max, const int64_t* pad_len, const __half* alibi, int alibi_stride,
                        cudaStream_t stream);
 
+
+// attention_tc.cu (tcgen05 prefill attention for long prompts)
+bool prefill_mha_tc_supported(int S, int D);
+int launch_prefill_mha_tc(const __half* q, const __half* kcache, const __half* vcache, __half* ctx, int B, int S, int H,
+                          int T_max, const int64_t* pad_len, const __half* alibi, int alibi_stride, cudaStream_t stream);
+
 }  // namespace eet

@@ -142,13 +142,17 @@ def test_prefill(S, mode):
     assert torch.allclose(got.float(), ref.float(), atol=4e-3, rtol=4e-3)
 
 
-@pytest.mark.parametrize("case", [(200, [70, 130], "pad"), (512, [0, 0], "plain"), (300, [0, 0], "alibi")])
+@pytest.mark.parametrize("case", [(200, [70, 130], "pad"), (512, [0, 0], "plain"), (300, [0, 0], "alibi"),
+                                  (96, [0, 95], "pad"), (128, [0, 0], "plain"), (129, [1, 128], "pad"),
+                                  (1024, [0, 0], "plain"), (1000, [0, 300], "pad"), (640, [0, 0], "alibi")])
 def test_prefill_long_prompts(case):
-    """Prompts of several 64-query tiles: left padding that swallows whole key blocks and whole query tiles
-    (their rows must come out zero), the configs[2] prompt length, and ALiBi across tiles."""
+    """Prompts of several query tiles (the tcgen05 kernel, 128 x 128 tiles, from 96 tokens on): left padding that
+    swallows whole key blocks and whole query tiles (their rows must come out zero), prompts of exactly one tile
+    and one token more, the configs[2] prompt length and the 1024 tokens of configs[4] (eight key blocks: both
+    rings and both score buffers wrap several times), and ALiBi across tiles."""
     from eet_b200._lib import check, lib
     S, pads, mode = case
-    B, H, D, T = 2, 2, 128, 520
+    B, H, D, T = 2, 2, 128, max(520, S + 8)
     gen = torch.Generator().manual_seed(S)
     q, k, v = (torch.randn(B, H, S, D, generator=gen).half() for _ in range(3))
     pad = torch.tensor(pads, dtype=torch.long) if mode == "pad" else None
@@ -169,7 +173,8 @@ def test_prefill_long_prompts(case):
     assert torch.allclose(got.float(), ref.float(), atol=4e-3, rtol=4e-3)
     if mode == "pad":
         for b, p_len in enumerate(pads):
-            assert float(got[b, :, :p_len].abs().max()) == 0.0   # rows inside the padding are zeroed
+            if p_len:
+                assert float(got[b, :, :p_len].abs().max()) == 0.0   # rows inside the padding are zeroed
 
 
 def test_decode_finishes_projection_sums_itself():
