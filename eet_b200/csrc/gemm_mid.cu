@@ -178,6 +178,11 @@ gemm_mid_kernel(const __grid_constant__ CUtensorMap tmap_x, GemmArgs a)
         while (w_fill < kMidNW && w_u < u1) issue_w();
     }
     if (warp == 1) {
+        // tcgen05.alloc blocks until the columns are free.  With programmatic dependent launch a CTA of the NEXT
+        // kernel can become resident beside a CTA of this one (shared memory permitting) and then waits here for
+        // tensor memory; that cannot deadlock, because no CTA of an earlier kernel ever waits for a later one: it
+        // runs to its dealloc.  (BN <= 64: 256 columns, two CTAs per SM; larger BN: 512 columns, and the shared-
+        // memory footprint of 100+ KiB keeps a second TMEM-holding CTA of the same kernel off the SM.)
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)),
                      "r"(kTmemCols)
                      : "memory");

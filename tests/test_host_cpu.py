@@ -122,3 +122,17 @@ def test_graph_mode_decode_step_refuses_to_run_past_the_cache():
 
 def test_device_status_codes_are_named():
     assert set(EET._STATUS_TEXT) == {1, 2, 3, 4, 5}
+
+
+def test_vocab_range_covers_the_vocabulary_in_whole_tiles():
+    for vocab, size in ((32000, 8), (32000, 4), (64000, 8), (1024, 8), (320, 2)):
+        ranges = [tp.vocab_range(vocab, r, size) for r in range(size)]
+        assert ranges[0][0] == 0 and ranges[-1][1] == vocab
+        assert all(ranges[i][1] == ranges[i + 1][0] for i in range(size - 1))
+        assert all(lo % 64 == 0 and hi % 64 == 0 and hi > lo for lo, hi in ranges)
+    widths = {hi - lo for lo, hi in (tp.vocab_range(32000, r, 8) for r in range(8))}
+    assert widths == {62 * 64, 63 * 64}          # 500 tiles over 8 ranks: uneven
+    with pytest.raises(ValueError):
+        tp.vocab_range(32001, 0, 2)
+    with pytest.raises(ValueError):
+        tp.vocab_range(128, 0, 4)

@@ -20,7 +20,7 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _worker(rank, world, port, q, small):
+def _worker(rank, world, port, q, small, batch=8):
     sys.path.insert(0, ROOT)
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
@@ -36,7 +36,7 @@ def _worker(rank, world, port, q, small):
             B, S, NEW, T = 2, 6, 4, 16
         else:
             cfg = tiny_config(layers=2, hidden=4096, heads=32, d_ff=11008, vocab=1024)
-            B, S, NEW, T = 8, 64, 4, 80
+            B, S, NEW, T = batch, 64, 4, 80
         sd = random_hf_state_dict(cfg, seed=9)
         eet_dict = modeling.convert_llama_weights({k: v.to(dev) for k, v in sd.items()}, torch.int8)
         gen = torch.Generator().manual_seed(1)
@@ -102,12 +102,12 @@ def _worker(rank, world, port, q, small):
         q.put((rank, traceback.format_exc()[-2000:]))
 
 
-def _run(world, small):
+def _run(world, small, batch=8):
     import torch.multiprocessing as mp
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = 29700 + (os.getpid() % 1000) + world
-    procs = [ctx.Process(target=_worker, args=(r, world, port, q, small)) for r in range(world)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q, small, batch)) for r in range(world)]
     for p in procs:
         p.start()
     results = []
@@ -135,3 +135,10 @@ def test_tensor_parallel_llama7b_width_matches_oracle(world):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     _run(world, small=False)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_gpu_fused_exchange_above_16_rows():
+    """Batch 32 (the Baichuan-13B decode batch): the fused exchange with more than 16 rows per inbox, fed by the
+    stream-K tensor-core GEMM instead of the skinny one, and the sharded lm_head's greedy kernel with 32 rows."""
+    _run(2, small=False, batch=32)
