@@ -430,6 +430,7 @@ def parity_check(tp, local, world, rank):
     if rank != 0:
         return None
     from oracle import ops
+    torch.set_num_threads(os.cpu_count() or 1)   # torchrun starts its workers with one OpenMP thread
     names = ("self_attn.qkv_proj", "self_attn.out_proj", "ffn.intermediate_0", "ffn.intermediate_1", "ffn.output")
     layers = []
     for i in range(2):

@@ -330,7 +330,7 @@ class _LmHead:
     """The lm_head of a causal LM.  By default the reference's: an fp16 torch.nn.Linear, replicated on every rank
     (modeling_llama.py:370-372, called at :471).  With int8=True (not in the reference) the weight is quantized
     like every other projection and runs through this library's W8A16 GEMM, and under tensor parallelism each rank
-    keeps only its vocabulary columns (whole 64-column tiles, tp.vocab_range): a decode step then reads 1/size of
+    keeps only its vocabulary columns (whole 128- or 64-column blocks, tp.vocab_range): a decode step then reads 1/size of
     half the bytes, and the greedy token is chosen from the GEMM's fp32 sums by one kernel that also settles the
     choice between the ranks (eet_lm_head_argmax)."""
 

@@ -151,14 +151,16 @@ def ff_range(d_ff, rank, size):
 
 
 def vocab_range(vocab, rank, size):
-    """Vocabulary columns [lo, hi) of the lm_head owned by `rank`: whole 64-column tiles of the packed weight,
-    unevenly when the tiles do not divide (32000 = 500 tiles over 8 ranks gives 62 or 63 tiles per rank)."""
+    """Vocabulary columns [lo, hi) of the lm_head owned by `rank`: whole 128-column strips (the unit of the
+    tensor-core GEMMs that compute prompt logits) when the vocabulary allows it, else 64-column tiles of the packed
+    weight; unevenly when they do not divide (32000 = 250 strips over 8 ranks gives 31 or 32 strips per rank)."""
     if vocab % 64:
         raise ValueError(f"vocabulary size {vocab} must be a multiple of 64 for an int8 lm_head")
-    tiles = vocab // 64
-    if tiles < size:
+    unit = 128 if vocab % 128 == 0 and vocab // 128 >= size else 64
+    units = vocab // unit
+    if units < size:
         raise ValueError(f"vocabulary of {vocab} has fewer 64-column tiles than the {size} ranks")
-    return 64 * (tiles * rank // size), 64 * (tiles * (rank + 1) // size)
+    return unit * (units * rank // size), unit * (units * (rank + 1) // size)
 
 
 def shard_plan(num_heads, d_ff, size):

@@ -131,7 +131,7 @@ def test_vocab_range_covers_the_vocabulary_in_whole_tiles():
         assert all(ranges[i][1] == ranges[i + 1][0] for i in range(size - 1))
         assert all(lo % 64 == 0 and hi % 64 == 0 and hi > lo for lo, hi in ranges)
     widths = {hi - lo for lo, hi in (tp.vocab_range(32000, r, 8) for r in range(8))}
-    assert widths == {62 * 64, 63 * 64}          # 500 tiles over 8 ranks: uneven
+    assert widths == {31 * 128, 32 * 128}        # 250 strips of 128 over 8 ranks: uneven
     with pytest.raises(ValueError):
         tp.vocab_range(32001, 0, 2)
     with pytest.raises(ValueError):
