@@ -422,6 +422,7 @@ bool prefill_mha_tc_supported(int S, int D)
 int launch_prefill_mha_tc(const __half* q, const __half* kcache, const __half* vcache, __half* ctx, int B, int S, int H,
                           int T_max, const int64_t* pad_len, const __half* alibi, int alibi_stride, cudaStream_t stream)
 {
+    EET_CHECK((long long)B * H <= 65535, "prefill attention: batch x heads = %lld exceeds the grid limit", (long long)B * H);
     CUtensorMap map_q, map_k, map_v;
     if (int rc = encode_rows_map(&map_q, q, S, (size_t)S, B * H, kPtQ)) return rc;
     if (int rc = encode_rows_map(&map_k, kcache, S, (size_t)T_max, B * H, kPtK)) return rc;
