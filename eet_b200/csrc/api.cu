@@ -212,7 +212,10 @@ int eet_gemm_w8a16(const void* A, const void* packedB, const void* scale, void* 
     EET_CHECK(epilogue == 0 || epilogue == 1, "eet_gemm_w8a16: unknown epilogue %d", epilogue);
     EET_CHECK(epilogue != 1 || residual != nullptr, "eet_gemm_w8a16: epilogue 1 needs a residual");
     const __half* res = epilogue == 1 ? (const __half*)residual : nullptr;
-    if (M <= mid_use_max_m() && gemm_mid_supported(M, N, K)) {
+    // Above 64 tokens a shape that the 256 x 256 kernel can spread over the machine (plain tiles or split-K
+    // clusters) goes there: one launch, epilogue fused, no fp32 scratch.
+    const bool tiles_first = M > 64 && gemm_tc_supported(M, N, K) && tc2_split(M, N, K) > 0;
+    if (!tiles_first && M <= mid_use_max_m() && gemm_mid_supported(M, N, K)) {
         // stream-K tensor-core kernel into the fp32 scratch, then one epilogue pass over all rows
         EET_CHECK(ws && aligned16(ws) && ws_bytes >= skinny_sum_bytes(M, N),
                   "eet_gemm_w8a16: workspace of %zu bytes is smaller than the %zu needed", ws_bytes, skinny_sum_bytes(M, N));

@@ -26,6 +26,7 @@
 // Numerics: exact integer weights as fp16, fp32 accumulation, one multiply by the fp16 scale, one rounding
 // to fp16 - the same as the skinny kernel's finalize step.
 #include <cuda.h>
+#include <cooperative_groups.h>
 
 #include "common.cuh"
 #include "kernels.h"
@@ -322,30 +323,106 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t* __rest
 }
 
 // ---------------------------------------------------------------------------------------------------
-// Large-M variant: 256 channels x 256 tokens per CTA.  Two accumulators (one per 128-channel half) fill all
-// 512 TMEM columns, and every activation tile fetched from L2 feeds twice as many MMAs as in the kernel
-// above, which halves the L2 -> shared-memory traffic per flop.  The three data streams have their own rings
-// so that each can run as far ahead as its buffer allows:
+// Large-M variant: 256 channels x 256 tokens per output tile.  Two accumulators (one per 128-channel half)
+// fill all 512 TMEM columns, and every activation tile fetched from L2 feeds twice as many MMAs as in the
+// kernel above, which halves the L2 -> shared-memory traffic per flop.  The three data streams have their own
+// rings so that each can run as far ahead as its buffer allows:
 //   activations : 3 x 32 KiB, one 2-D TMA copy per k-block            (warp 0)
 //   int8 weights: 4 x 16 KiB, four 4 KiB bulk copies per k-block      (warp 6)
 //   fp16 weights: 2 x 32 KiB (k-block x two 128-channel halves), written by warps 2-5 / 7-10, read by tcgen05.mma
 // One commit per k-block ("done", ring of 6 = lcm of the ring depths) releases the activation stage to its
 // producer and the fp16 stage to the transform warps: the issuing thread pays for two waits, eight MMAs and
 // one commit per k-block.
+//
+// Two ways to spread the tiles over the SMs:
+//
+// (a) Persistent CTAs (gridDim.z == 1), one per SM (fewer when there are fewer tiles): CTA i takes tiles i, i + G,
+//     i + 2G, ... so that the CTAs of a wave walk the k-blocks in step - CTAs that read the same activation or
+//     weight tile at the same time are served together by the L2.  The rings and all phase counters run on
+//     across tiles: while the transform warps are busy with a tile's epilogue, the producers already fetch the
+//     next tile's first k-blocks.  The epilogue's fp16 staging tiles live in the fp16 weight ring, which is idle
+//     exactly then (all MMAs of the tile have completed, the next conversions come after).
+//     Two ways of cutting the work so that no SM idles through the last, partial wave were built and measured
+//     on 148 SMs, and dropped: (i) textbook stream-K (equal contiguous ranges of (tile, k-block) pairs, partial
+//     accumulators handed on through a global scratch) ran 1.3x slower per k-block, because the CTAs no longer
+//     read the same tiles at the same time (4096^2, M = 4096: 145 us against 109); (ii) whole tiles in waves and
+//     only the left-over tiles cut along K into pieces that keep the k-blocks in step gained 0-3 % (4096 x 12288,
+//     M = 4096: 328 us against 330; 11008 x 4096: 267 against 274) - exporting and importing 256 KiB accumulators
+//     costs what the shorter wave saves.
+//
+// (b) Split-K over a thread-block cluster (gridDim.z = cluster size S = 2, 3 or 4) for shapes with fewer tiles
+//     than SMs: the S CTAs of a cluster share one output tile (blockIdx.x, blockIdx.y) and each walks 1/S of the
+//     k-blocks.  The partial accumulators meet through distributed shared memory, never through global memory:
+//     the tile's eight 32-token blocks are dealt out to the ranks (block b belongs to rank b % S), every CTA
+//     stores its partial of a foreign block into the owner's shared memory (the operand rings are idle by then;
+//     a warp's store instruction covers 512 contiguous bytes), and after one cluster barrier each owner adds
+//     the S - 1 partials to its own accumulator in rank order and runs the usual epilogue for its blocks only.
 // ---------------------------------------------------------------------------------------------------
 constexpr int kTc2Threads = 352;   // X producer, MMA issuer, 4 + 4 transform/epilogue warps, W producer
 constexpr int kTc2NX = 3, kTc2NW = 4, kTc2NH = 2, kTc2ND = 6;
 constexpr int kTc2XBytes = 256 * 128, kTc2WBytes = 4 * kTileBytes, kTc2HBytes = 128 * 128;   // H: one half
 constexpr int kTc2Smem = kTc2NX * kTc2XBytes + kTc2NW * kTc2WBytes + kTc2NH * 2 * kTc2HBytes;
+constexpr int kTc2RedBlock = 256 * 128;               // one partial block: 256 channels x 32 tokens fp32
+constexpr int kTc2StageBytes = 2 * 2 * kEpiStageHalves * 2;   // the epilogue's fp16 staging tiles (two per group)
+// cluster mode: partial blocks received by one CTA (blocks owned, at most ceil(8 / S), x (S - 1) senders) follow
+// the staging tiles at the start of the activation ring
+static_assert(kTc2StageBytes + 6 * kTc2RedBlock <= kTc2Smem, "partials of S = 3 and S = 4 must fit behind the staging tiles");
+static_assert(kTc2StageBytes <= kTc2NH * 2 * kTc2HBytes, "stream-K mode stages its output in the fp16 weight ring");
+
+// Barrier of the 256 transform/epilogue threads of the 256 x 256 kernel that also ORs a predicate over them:
+// every thread gets the same answer, so a decision taken on it cannot split the group before a later barrier.
+__device__ __forceinline__ bool epi_bar_or(bool pred)
+{
+    uint32_t out;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p, q;\n\t"
+        "setp.ne.u32 q, %1, 0;\n\t"
+        "bar.red.or.pred p, 3, 256, q;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "}\n"
+        : "=r"(out)
+        : "r"((uint32_t)pred)
+        : "memory");
+    return out != 0;
+}
 
 struct Tc2Smem {
     uint64_t x_full[kTc2NX];
     uint64_t w_full[kTc2NW], w_empty[kTc2NW];
     uint64_t h_ready[kTc2NH];     // both halves of a k-block are written (8 transform warps)
     uint64_t done[kTc2ND];        // the MMAs of a k-block have completed
-    uint64_t accum;
+    uint64_t accum;               // all MMAs of a segment have completed
+    uint64_t acc_free;            // the 8 epilogue warps have read the segment's accumulators
     uint32_t tmem_base;
     volatile int abort;
+};
+
+// One CTA's share of the work: `nseg` segments, processed in order.
+struct Tc2Seg {
+    int tile, kb0, kb1;
+    bool cluster;   // a k-range of a tile shared with the other CTAs of the cluster
+};
+
+struct Tc2Work {
+    int KT, G, i, nseg, cluster_kb0, cluster_kb1, cluster_tile;
+
+    __device__ Tc2Seg seg(int p) const
+    {
+        Tc2Seg s;
+        if (cluster_tile >= 0) {
+            s.tile = cluster_tile;
+            s.kb0 = cluster_kb0;
+            s.kb1 = cluster_kb1;
+            s.cluster = true;
+            return s;
+        }
+        s.tile = p * G + i;
+        s.kb0 = 0;
+        s.kb1 = KT;
+        s.cluster = false;
+        return s;
+    }
 };
 
 __global__ void __launch_bounds__(kTc2Threads, 1)
@@ -359,10 +436,29 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t* __res
     uint8_t* h_ring = base + kTc2NX * kTc2XBytes;             // 1024-byte aligned tiles (swizzled)
     uint8_t* w_ring = h_ring + kTc2NH * 2 * kTc2HBytes;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n0 = blockIdx.x * 256;
-    const int m0 = blockIdx.y * 256;
-    const int KT = K / kTile;
+    const int S = (int)gridDim.z, rank = (int)blockIdx.z;
+    const int tiles_n = N / 256, tiles_m = (M + 255) / 256;
 
+    Tc2Work wk;
+    wk.KT = K / kTile;
+    wk.G = (int)gridDim.x;
+    wk.i = (int)blockIdx.x;
+    wk.cluster_tile = -1;
+    wk.cluster_kb0 = wk.cluster_kb1 = 0;
+    if (S > 1) {
+        // cluster mode: the cluster is the gridDim.z CTAs of tile (blockIdx.x, blockIdx.y)
+        wk.cluster_tile = (int)(blockIdx.y * tiles_n + blockIdx.x);
+        wk.cluster_kb0 = (int)((long long)wk.KT * rank / S);
+        wk.cluster_kb1 = (int)((long long)wk.KT * (rank + 1) / S);
+        wk.nseg = 1;
+    }
+    else {
+        const int tiles = tiles_n * tiles_m;
+        wk.nseg = (tiles - wk.i + wk.G - 1) / wk.G;   // tiles i, i + G, ...
+    }
+    const int nseg = wk.nseg;
+
+    pdl_launch_dependents();
     if (threadIdx.x == 0) {
         for (int s = 0; s < kTc2NX; ++s) mbar_init(&sm.x_full[s], 1);
         for (int s = 0; s < kTc2ND; ++s) mbar_init(&sm.done[s], 1);
@@ -372,6 +468,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t* __res
         }
         for (int s = 0; s < kTc2NH; ++s) mbar_init(&sm.h_ready[s], 8);
         mbar_init(&sm.accum, 1);
+        mbar_init(&sm.acc_free, 8);
         sm.abort = 0;
         mbar_fence_init();
     }
@@ -385,44 +482,62 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t* __res
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = sm.tmem_base;
+    bool epi_live = false;   // cluster mode: this epilogue thread has a complete accumulator to reduce
 
     if (warp == 0) {
         // ------------------------------------------------------------------ activation producer
         if (lane == 0) {
             // (ring positions are counters: this loop is one thread's chain of dependent instructions)
-            int s = 0, d = 0;      // d: slot of done[] for k-block kb - NX
+            int s = 0, d = 0, it = 0;      // d: slot of done[] for k-block it - NX
             uint32_t phd = 0;
-            for (int kb = 0; kb < KT; ++kb) {
-                if (kb >= kTc2NX) {
-                    if (!tc_wait(&sm.done[d], phd, &sm.abort)) break;
-                    if (++d == kTc2ND) {
-                        d = 0;
-                        phd ^= 1;
+            bool ok = true;
+            pdl_wait();            // the activations are the preceding kernel's output (the weights are not)
+            for (int p = 0; p < nseg && ok; ++p) {
+                const Tc2Seg sg = wk.seg(p);
+                const int m0 = (sg.tile / tiles_n) * 256;
+                for (int kb = sg.kb0; kb < sg.kb1; ++kb, ++it) {
+                    if (it >= kTc2NX) {
+                        if (!tc_wait(&sm.done[d], phd, &sm.abort)) {
+                            ok = false;
+                            break;
+                        }
+                        if (++d == kTc2ND) {
+                            d = 0;
+                            phd ^= 1;
+                        }
                     }
+                    mbar_arrive_expect_tx(&sm.x_full[s], (uint32_t)kTc2XBytes);
+                    tma_load_2d(x_ring + (size_t)s * kTc2XBytes, &tmap_x, kb * kTile, m0, &sm.x_full[s]);
+                    if (++s == kTc2NX) s = 0;
                 }
-                mbar_arrive_expect_tx(&sm.x_full[s], (uint32_t)kTc2XBytes);
-                tma_load_2d(x_ring + (size_t)s * kTc2XBytes, &tmap_x, kb * kTile, m0, &sm.x_full[s]);
-                if (++s == kTc2NX) s = 0;
             }
         }
     }
     else if (warp == 6) {
         // ------------------------------------------------------------------ int8 weight producer
         if (lane == 0) {
-            int s = 0;
+            int s = 0, it = 0;
             uint32_t ph = 1;
-            const uint8_t* w0 = Bw + (size_t)(n0 / kTile) * KT * kTileBytes;
-            for (int kb = 0; kb < KT; ++kb, w0 += kTileBytes) {
-                if (kb >= kTc2NW && !tc_wait(&sm.w_empty[s], ph, &sm.abort)) break;
-                mbar_arrive_expect_tx(&sm.w_full[s], (uint32_t)kTc2WBytes);
-                uint8_t* dst = w_ring + (size_t)s * kTc2WBytes;
+            bool ok = true;
+            for (int p = 0; p < nseg && ok; ++p) {
+                const Tc2Seg sg = wk.seg(p);
+                const int n0 = (sg.tile % tiles_n) * 256;
+                const uint8_t* w0 = Bw + ((size_t)(n0 / kTile) * wk.KT + sg.kb0) * kTileBytes;
+                for (int kb = sg.kb0; kb < sg.kb1; ++kb, ++it, w0 += kTileBytes) {
+                    if (it >= kTc2NW && !tc_wait(&sm.w_empty[s], ph, &sm.abort)) {
+                        ok = false;
+                        break;
+                    }
+                    mbar_arrive_expect_tx(&sm.w_full[s], (uint32_t)kTc2WBytes);
+                    uint8_t* dst = w_ring + (size_t)s * kTc2WBytes;
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    bulk_g2s(dst + i * kTileBytes, w0 + (size_t)i * KT * kTileBytes, kTileBytes, &sm.w_full[s]);
-                }
-                if (++s == kTc2NW) {
-                    s = 0;
-                    ph ^= 1;
+                    for (int i = 0; i < 4; ++i) {
+                        bulk_g2s(dst + i * kTileBytes, w0 + (size_t)i * wk.KT * kTileBytes, kTileBytes, &sm.w_full[s]);
+                    }
+                    if (++s == kTc2NW) {
+                        s = 0;
+                        ph ^= 1;
+                    }
                 }
             }
         }
@@ -433,32 +548,43 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t* __res
             constexpr uint32_t idesc = umma_idesc_f16(128, 256);
             const uint64_t b_desc0 = umma_desc_sw128(smem_u32(x_ring));
             const uint64_t a_desc0 = umma_desc_sw128(smem_u32(h_ring));
-            int sx = 0, sd = 0;
+            int sx = 0, sd = 0, it = 0;
             uint32_t phx = 0;
-            for (int kb = 0; kb < KT; ++kb) {
-                const int sh = kb & 1;
-                if (!tc_wait(&sm.x_full[sx], phx, &sm.abort)) break;
-                if (!tc_wait(&sm.h_ready[sh], (uint32_t)((kb >> 1) & 1), &sm.abort)) break;
+            bool ok = true;
+            for (int p = 0; p < nseg && ok; ++p) {
+                const Tc2Seg sg = wk.seg(p);
+                // the accumulators are overwritten: the epilogue of the previous segment must have read them
+                if (p > 0 && !tc_wait(&sm.acc_free, (uint32_t)((p - 1) & 1), &sm.abort)) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint64_t b_desc = b_desc0 + (uint64_t)(sx * (kTc2XBytes >> 4));
-                const uint64_t a0 = a_desc0 + (uint64_t)(sh * (2 * kTc2HBytes >> 4));
-                const uint64_t a1 = a0 + (uint64_t)(kTc2HBytes >> 4);
-                umma_f16(tmem, a0, b_desc, idesc, kb != 0);
-                umma_f16(tmem, a0 + 2, b_desc + 2, idesc, true);
-                umma_f16(tmem, a0 + 4, b_desc + 4, idesc, true);
-                umma_f16(tmem, a0 + 6, b_desc + 6, idesc, true);
-                umma_f16(tmem + 256, a1, b_desc, idesc, kb != 0);
-                umma_f16(tmem + 256, a1 + 2, b_desc + 2, idesc, true);
-                umma_f16(tmem + 256, a1 + 4, b_desc + 4, idesc, true);
-                umma_f16(tmem + 256, a1 + 6, b_desc + 6, idesc, true);
-                umma_commit(&sm.done[sd]);
-                if (++sd == kTc2ND) sd = 0;
-                if (++sx == kTc2NX) {
-                    sx = 0;
-                    phx ^= 1;
+                for (int kb = sg.kb0; kb < sg.kb1; ++kb, ++it) {
+                    const int sh = it & 1;
+                    if (!tc_wait(&sm.x_full[sx], phx, &sm.abort) ||
+                        !tc_wait(&sm.h_ready[sh], (uint32_t)((it >> 1) & 1), &sm.abort)) {
+                        ok = false;
+                        break;
+                    }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint64_t b_desc = b_desc0 + (uint64_t)(sx * (kTc2XBytes >> 4));
+                    const uint64_t a0 = a_desc0 + (uint64_t)(sh * (2 * kTc2HBytes >> 4));
+                    const uint64_t a1 = a0 + (uint64_t)(kTc2HBytes >> 4);
+                    const bool acc = kb != sg.kb0;
+                    umma_f16(tmem, a0, b_desc, idesc, acc);
+                    umma_f16(tmem, a0 + 2, b_desc + 2, idesc, true);
+                    umma_f16(tmem, a0 + 4, b_desc + 4, idesc, true);
+                    umma_f16(tmem, a0 + 6, b_desc + 6, idesc, true);
+                    umma_f16(tmem + 256, a1, b_desc, idesc, acc);
+                    umma_f16(tmem + 256, a1 + 2, b_desc + 2, idesc, true);
+                    umma_f16(tmem + 256, a1 + 4, b_desc + 4, idesc, true);
+                    umma_f16(tmem + 256, a1 + 6, b_desc + 6, idesc, true);
+                    umma_commit(&sm.done[sd]);
+                    if (++sd == kTc2ND) sd = 0;
+                    if (++sx == kTc2NX) {
+                        sx = 0;
+                        phx ^= 1;
+                    }
                 }
+                if (ok) umma_commit(&sm.accum);
             }
-            umma_commit(&sm.accum);
         }
     }
     else {
@@ -468,73 +594,172 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t* __res
         // convert a k-block in the time the tensor core needs for it.
         const int grp = (warp >= 7) ? 1 : 0;
         const int tw = (warp - (grp ? 7 : 2)) * 32 + lane;  // 0..127 within the group
-        int sw = 0, d = 0;     // d: slot of done[] for k-block kb - NH
+        const int lane_base = (warp & 3) * 32;              // the TMEM lanes this warp may read
+        const int ch = grp * 128 + lane_base + lane;        // this thread's channel of the tile
+        int sw = 0, d = 0, it = 0;     // d: slot of done[] for k-block it - NH
         uint32_t phw = 0, phd = 0;
-        for (int kb = 0; kb < KT; ++kb) {
-            if (!tc_wait(&sm.w_full[sw], phw, &sm.abort)) break;
-            const uint8_t* w8 = w_ring + (size_t)sw * kTc2WBytes;
-            const int sh = kb & 1;
-            if (kb >= kTc2NH) {
-                if (!tc_wait(&sm.done[d], phd, &sm.abort)) break;
-                if (++d == kTc2ND) {
-                    d = 0;
-                    phd ^= 1;
+        bool ok = true;
+        for (int p = 0; p < nseg && ok; ++p) {
+            const Tc2Seg sg = wk.seg(p);
+            for (int kb = sg.kb0; kb < sg.kb1; ++kb, ++it) {
+                if (!tc_wait(&sm.w_full[sw], phw, &sm.abort)) {
+                    ok = false;
+                    break;
+                }
+                const uint8_t* w8 = w_ring + (size_t)sw * kTc2WBytes;
+                const int sh = it & 1;
+                if (it >= kTc2NH) {
+                    if (!tc_wait(&sm.done[d], phd, &sm.abort)) {
+                        ok = false;
+                        break;
+                    }
+                    if (++d == kTc2ND) {
+                        d = 0;
+                        phd ^= 1;
+                    }
+                }
+                uint8_t* wh = h_ring + (size_t)(sh * 2 + grp) * kTc2HBytes;
+#pragma unroll
+                for (int pass = 0; pass < 4; ++pass) {
+                    const int r = pass * 32 + (tw >> 2);   // channel row of this half, 0..127
+                    const int qd = tw & 3;
+                    const uint4 raw = *reinterpret_cast<const uint4*>(w8 + (grp * 128 + r) * 64 + qd * 16);
+                    uint4 o0, o1;
+                    cvt_u8x4_to_f16x4(raw.x, o0.x, o0.y);
+                    cvt_u8x4_to_f16x4(raw.y, o0.z, o0.w);
+                    cvt_u8x4_to_f16x4(raw.z, o1.x, o1.y);
+                    cvt_u8x4_to_f16x4(raw.w, o1.z, o1.w);
+                    uint8_t* row = wh + r * 128;
+                    *reinterpret_cast<uint4*>(row + (((2 * qd) ^ (r & 7)) << 4)) = o0;
+                    *reinterpret_cast<uint4*>(row + (((2 * qd + 1) ^ (r & 7)) << 4)) = o1;
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(&sm.h_ready[sh]);
+                    mbar_arrive(&sm.w_empty[sw]);
+                }
+                if (++sw == kTc2NW) {
+                    sw = 0;
+                    phw ^= 1;
                 }
             }
-            uint8_t* wh = h_ring + (size_t)(sh * 2 + grp) * kTc2HBytes;
-#pragma unroll
-            for (int pass = 0; pass < 4; ++pass) {
-                const int r = pass * 32 + (tw >> 2);   // channel row of this half, 0..127
-                const int qd = tw & 3;
-                const uint4 raw = *reinterpret_cast<const uint4*>(w8 + (grp * 128 + r) * 64 + qd * 16);
-                uint4 o0, o1;
-                cvt_u8x4_to_f16x4(raw.x, o0.x, o0.y);
-                cvt_u8x4_to_f16x4(raw.y, o0.z, o0.w);
-                cvt_u8x4_to_f16x4(raw.z, o1.x, o1.y);
-                cvt_u8x4_to_f16x4(raw.w, o1.z, o1.w);
-                uint8_t* row = wh + r * 128;
-                *reinterpret_cast<uint4*>(row + (((2 * qd) ^ (r & 7)) << 4)) = o0;
-                *reinterpret_cast<uint4*>(row + (((2 * qd + 1) ^ (r & 7)) << 4)) = o1;
-            }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            __syncwarp();
-            if (lane == 0) {
-                mbar_arrive(&sm.h_ready[sh]);
-                mbar_arrive(&sm.w_empty[sw]);
-            }
-            if (++sw == kTc2NW) {
-                sw = 0;
-                phw ^= 1;
-            }
-        }
+            if (!ok) break;
 
-        // ---- epilogue: TMEM lane = channel within the half, columns = tokens; group g takes accumulator g ----
-        // every epilogue warp gets here (the waits are bounded); the barrier makes the abort decision uniform
-        tc_wait(&sm.accum, 0, &sm.abort);
-        if (grp == 0) {
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-        }
-        else {
-            asm volatile("bar.sync 2, 128;" ::: "memory");
-        }
-        if (sm.abort == 0) {
+            // ---- end of the segment: every epilogue warp gets here (the waits are bounded); the OR-reducing
+            // barrier gives all 256 epilogue threads the same verdict, whoever saw the abort flag first ----
+            tc_wait(&sm.accum, (uint32_t)(p & 1), &sm.abort);
+            if (epi_bar_or(sm.abort != 0)) {
+                ok = false;
+                break;
+            }
+            if (sg.cluster) {   // cluster split: the epilogue follows the cluster barriers below
+                epi_live = true;
+                break;
+            }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const int lane_base = (warp & 3) * 32;
+            pdl_wait();   // the output and the residual belong to the dependency chain
+            const int n0 = (sg.tile % tiles_n) * 256, m0 = (sg.tile / tiles_n) * 256;
+            {
+                const float sc = __half2float(scale[n0 + ch]);
+                __half* stage = reinterpret_cast<__half*>(h_ring) + grp * 2 * kEpiStageHalves;
+                int blk = 0;
+#pragma unroll 1
+                for (int b = 0; b < 8; ++b, ++blk) {
+                    const int c0 = 32 * b;
+                    if (m0 + c0 >= M) break;
+                    uint32_t v[32];
+                    tmem_ld32(tmem + ((uint32_t)lane_base << 16) + (uint32_t)(grp * 256 + c0), v);
+                    if (grp == 0) {
+                        epilogue_block<1>(v, sc, stage + (blk & 1) * kEpiStageHalves, lane_base + lane, tw, C, residual, m0 + c0,
+                                          M, N, n0);
+                    }
+                    else {
+                        epilogue_block<2>(v, sc, stage + (blk & 1) * kEpiStageHalves, lane_base + lane, tw, C, residual, m0 + c0,
+                                          M, N, n0 + 128);
+                    }
+                }
+                // The staging tiles lie in this group's own part of the fp16 weight ring: its next conversions
+                // must not start before every thread of the group has read its rows of the last tile.
+                if (grp == 0) {
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                }
+                else {
+                    asm volatile("bar.sync 2, 128;" ::: "memory");
+                }
+            }
+            // accumulators read: the next segment's MMAs may overwrite them
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sm.acc_free);
+        }
+    }
+
+    if (S > 1) {
+        // ---- cluster split: reduce the S partial accumulators through distributed shared memory, then the
+        // epilogue: TMEM lane = channel within the half, columns = tokens; group g takes accumulator g ----
+        const bool epi_warp = (warp >= 2 && warp <= 5) || (warp >= 7 && warp <= 10);
+        const int grp = (warp >= 7) ? 1 : 0;
+        const int tw = (warp - (grp ? 7 : 2)) * 32 + lane;   // 0..127 within the group
+        const int lane_base = (warp & 3) * 32;
+        const int ch = grp * 128 + lane_base + lane;          // this thread's channel of the tile
+        const int n0 = blockIdx.x * 256, m0 = blockIdx.y * 256;
+        uint8_t* red = base + kTc2StageBytes;
+        // All CTAs of the cluster have completed their MMAs: their rings may be overwritten.
+        cooperative_groups::this_cluster().sync();
+        if (epi_warp && epi_live) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            for (int b = 0; b < 8; ++b) {
+                if (m0 + 32 * b >= M) break;
+                const int owner = b % S;
+                if (owner == rank) continue;
+                uint32_t v[32];
+                tmem_ld32(tmem + ((uint32_t)lane_base << 16) + (uint32_t)(grp * 256 + 32 * b), v);
+                // a partial block is laid out [4-token chunk][channel][16 bytes]: the 32 lanes of a warp store 512
+                // contiguous bytes per instruction, and the owner reads them back the same way
+                const int slot = (b / S) * (S - 1) + (rank < owner ? rank : rank - 1);
+                const uint32_t local = smem_u32(red + (size_t)slot * kTc2RedBlock + (size_t)ch * 16);
+                uint32_t remote;
+                asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"((uint32_t)owner));
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    asm volatile("st.shared::cluster.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(remote + (uint32_t)(j * 256 * 16)),
+                                 "r"(v[4 * j]), "r"(v[4 * j + 1]), "r"(v[4 * j + 2]), "r"(v[4 * j + 3])
+                                 : "memory");
+                }
+            }
+        }
+        // the partials of this CTA's blocks have arrived
+        cooperative_groups::this_cluster().sync();
+        if (epi_warp && epi_live) {
+            pdl_wait();   // the output (and the residual) belong to the dependency chain
             __half* stage = reinterpret_cast<__half*>(x_ring) + grp * 2 * kEpiStageHalves;
-            const float sc = __half2float(scale[n0 + grp * 128 + lane_base + lane]);
+            const float sc = __half2float(scale[n0 + ch]);
             int blk = 0;
 #pragma unroll 1
-            for (int c0 = 0; c0 < 256; c0 += 32, ++blk) {
+            for (int b = rank; b < 8; b += S, ++blk) {
+                const int c0 = 32 * b;
                 if (m0 + c0 >= M) break;
                 uint32_t v[32];
                 tmem_ld32(tmem + ((uint32_t)lane_base << 16) + (uint32_t)(grp * 256 + c0), v);
+                for (int src = 0; src < S - 1; ++src) {
+                    const uint8_t* p = red + (size_t)((b / S) * (S - 1) + src) * kTc2RedBlock + (size_t)ch * 16;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const uint4 q = *reinterpret_cast<const uint4*>(p + j * 256 * 16);
+                        v[4 * j] = __float_as_uint(__uint_as_float(v[4 * j]) + __uint_as_float(q.x));
+                        v[4 * j + 1] = __float_as_uint(__uint_as_float(v[4 * j + 1]) + __uint_as_float(q.y));
+                        v[4 * j + 2] = __float_as_uint(__uint_as_float(v[4 * j + 2]) + __uint_as_float(q.z));
+                        v[4 * j + 3] = __float_as_uint(__uint_as_float(v[4 * j + 3]) + __uint_as_float(q.w));
+                    }
+                }
                 if (grp == 0) {
-                    epilogue_block<1>(v, sc, stage + (blk & 1) * kEpiStageHalves, lane_base + lane, tw, C, residual, m0 + c0,
-                                      M, N, n0);
+                    epilogue_block<1>(v, sc, stage + (blk & 1) * kEpiStageHalves, lane_base + lane, tw, C, residual, m0 + c0, M, N,
+                                      n0);
                 }
                 else {
-                    epilogue_block<2>(v, sc, stage + (blk & 1) * kEpiStageHalves, lane_base + lane, tw, C, residual, m0 + c0,
-                                      M, N, n0 + 128);
+                    epilogue_block<2>(v, sc, stage + (blk & 1) * kEpiStageHalves, lane_base + lane, tw, C, residual, m0 + c0, M, N,
+                                      n0 + 128);
                 }
             }
         }
@@ -591,6 +816,66 @@ int launch_tc(const CUtensorMap& map, const uint8_t* B, const __half* scale, __h
 // leave most SMs idle, so the skinny kernel serves those.
 constexpr int kTcMinM = 65;
 
+// Clusters of `split` CTAs of the 256 x 256 kernel that can be resident at once (0: that cluster size cannot be
+// launched), asked of the occupancy calculator once per device and size.
+static int tc2_max_clusters(int split)
+{
+    static int cached[64][5] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+    dev &= 63;
+    if (cached[dev][split] == 0) {
+        const size_t smem = (size_t)kTc2Smem + 1024;
+        int n = 0;
+        if (cudaFuncSetAttribute(gemm_tc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess) {
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3(1, 1, split);
+            cfg.blockDim = dim3(kTc2Threads, 1, 1);
+            cfg.dynamicSmemBytes = smem;
+            cudaLaunchAttribute attr[1];
+            attr[0].id = cudaLaunchAttributeClusterDimension;
+            attr[0].val.clusterDim.x = 1;
+            attr[0].val.clusterDim.y = 1;
+            attr[0].val.clusterDim.z = split;
+            cfg.attrs = attr;
+            cfg.numAttrs = 1;
+            if (cudaOccupancyMaxActiveClusters(&n, gemm_tc2_kernel, &cfg) != cudaSuccess) {
+                (void)cudaGetLastError();
+                n = 0;
+            }
+        }
+        cached[dev][split] = n > 0 ? n : -1;
+    }
+    return cached[dev][split] > 0 ? cached[dev][split] : 0;
+}
+
+// How the 256 x 256 kernel would run this shape: 0 = not at all, 1 = whole tiles on persistent CTAs, 2/3/4 = the
+// k-blocks of a tile split over a cluster of that size.  Whole tiles need most of the machine's worth of them
+// (120); below that the largest split is taken that puts at least 96 CTAs to work, whose clusters are all
+// resident at once and which still leaves each CTA four k-blocks.
+int tc2_split(int M, int N, int K)
+{
+    if (N % 256 != 0 || M < kTcMinM) return 0;
+    static int forced = -2;
+    if (forced == -2) {
+        const char* e = getenv("EET_TC2_SPLIT");
+        forced = e ? atoi(e) : -1;
+    }
+    const long long tiles = (long long)(N / 256) * ((M + 255) / 256);
+    if (forced == 0) return tiles >= 120 ? 1 : 0;
+    if (tiles >= 120) return 1;
+    const int KT = K / kTile;
+    static const int sizes[3] = {4, 3, 2};
+    for (int i = 0; i < 3; ++i) {
+        const int sp = sizes[i];
+        if (forced > 0 && sp != forced) continue;
+        // (clusters of 8 were measured too: the all-to-all of 7/8 of every accumulator costs more than the
+        // shorter k-loops save)
+        if (KT / sp >= 4 && tiles * sp >= 96 && tiles <= tc2_max_clusters(sp)) return sp;
+    }
+    return 0;
+}
+
 bool gemm_tc_supported(int M, int N, int K)
 {
     return M >= kTcMinM && N % 128 == 0 && K % 64 == 0;
@@ -602,7 +887,9 @@ int launch_gemm_tc(const __half* A, const uint8_t* B, const __half* scale, __hal
     EET_CHECK(gemm_tc_supported(M, N, K), "tensor-core GEMM: needs M >= 65, N %% 128 == 0, K %% 64 == 0");
     EncodeTiledFn encode = encode_tiled_fn();
     EET_CHECK(encode != nullptr, "tensor-core GEMM: cuTensorMapEncodeTiled is not available from the driver");
-    const int bn = (M > 128) ? 256 : (M > 64 ? 128 : 64);
+    const int split = tc2_split(M, N, K);
+    // token rows per activation tile: always 256 for the 256 x 256 kernel (rows past M read as zeros)
+    const int bn = (split > 0 || M > 128) ? 256 : (M > 64 ? 128 : 64);
     CUtensorMap map;
     const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)M};
     const cuuint64_t strides[1] = {(cuuint64_t)K * sizeof(__half)};
@@ -612,8 +899,9 @@ int launch_gemm_tc(const __half* A, const uint8_t* B, const __half* scale, __hal
                                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     EET_CHECK(rc == CUDA_SUCCESS, "tensor-core GEMM: cuTensorMapEncodeTiled failed with code %d", (int)rc);
-    // the 256 x 256 tiles pay off once there are enough of them to fill most of the machine
-    if (N % 256 == 0 && (long long)(N / 256) * ((M + 255) / 256) >= 120) {
+    // the 256 x 256 tiles pay off once there are enough of them to fill most of the machine - on a grid of
+    // persistent CTAs, or with the k-blocks of a tile split over a cluster
+    if (split > 0) {
         static bool attr_set2[64] = {};
         int dev = 0;
         EET_CUDA(cudaGetDevice(&dev));
@@ -623,9 +911,28 @@ int launch_gemm_tc(const __half* A, const uint8_t* B, const __half* scale, __hal
             EET_CUDA(cudaFuncSetAttribute(gemm_tc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
             attr_set2[dev] = true;
         }
-        dim3 grid(N / 256, (M + 255) / 256);
-        gemm_tc2_kernel<<<grid, kTc2Threads, smem, stream>>>(map, B, scale, C, residual, M, N, K);
-        EET_LAUNCH_CHECK();
+        cudaLaunchConfig_t cfg = {};
+        if (split == 1) {
+            // one persistent CTA per SM, fewer when there are fewer tiles
+            const long long tiles = (long long)(N / 256) * ((M + 255) / 256);
+            cfg.gridDim = dim3((unsigned)(tiles < sm_count() ? tiles : sm_count()), 1, 1);
+        }
+        else {
+            cfg.gridDim = dim3(N / 256, (M + 255) / 256, split);
+        }
+        cfg.blockDim = dim3(kTc2Threads, 1, 1);
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[2];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 1;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = split;
+        attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[1].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 2;
+        EET_CUDA(cudaLaunchKernelEx(&cfg, gemm_tc2_kernel, map, B, scale, C, residual, M, N, K));
         return 0;
     }
     if (bn == 256) return launch_tc<256>(map, B, scale, C, residual, M, N, K, stream);

@@ -30,6 +30,7 @@ int launch_gemm_skinny(const GemmArgs& a, cudaStream_t stream);
 
 // gemm_tc.cu (tcgen05 / TMEM)
 bool gemm_tc_supported(int M, int N, int K);
+int tc2_split(int M, int N, int K);  // 0: the 256 x 256 kernel does not take this shape; else its split-K cluster size
 int launch_gemm_tc(const __half* A, const uint8_t* B, const __half* scale, __half* C, const __half* residual, int M,
                    int N, int K, cudaStream_t stream);
 

@@ -255,3 +255,57 @@ def test_llama7b_projection_shapes_across_the_kernel_regimes(KN, M):
     res = torch.randn(M, N, generator=gen).half()
     yr = _run(x, q, s, residual=res)
     assert torch.allclose(yr[rows].float(), ops.add_residual(y[rows], res[rows]).float(), rtol=2e-3, atol=2e-3)
+
+
+@pytest.mark.parametrize("KNM", [(1088, 6144, 300), (832, 8192, 130), (2048, 2560, 700), (4096, 4096, 300), (4096, 4096, 512),
+                                 (4096, 11008, 200), (11008, 4096, 700)])
+def test_split_k_cluster_tiles(KNM):
+    """Shapes with fewer 256 x 256 tiles than SMs (24 to 48 of them): the k-blocks of a tile are split over a
+    cluster of 2, 3 or 4 CTAs whose partial accumulators meet through distributed shared memory.  Uneven k-splits
+    (17 and 13 k-blocks), a ragged last token tile (blocks past M are neither sent nor reduced), with and without
+    the residual.  Every element against an fp32 matmul of
+    the dequantized weights run by torch on the GPU (checker only), sampled rows against the fp64 oracle."""
+    K, N, M = KNM
+    gen = torch.Generator().manual_seed(K + N + M)
+    q = torch.randint(-128, 128, (K, N), generator=gen, dtype=torch.int8)
+    s = (torch.rand(N, generator=gen) * 3e-4 + 1e-4).half()
+    x = torch.randn(M, K, generator=gen).half()
+    y = _run(x, q, s)
+    rows = torch.tensor(sorted({0, 1, 31, 32, 63, 64, 95, 127, 128, 129, M // 2, M - 2, M - 1} & set(range(M))))
+    ref = ops.gemm_w8a16_fp32(x[rows], q, s)
+    assert ((y[rows].double() - ref).abs() <= 1e-2 * ref.abs().amax(1, keepdim=True)).all()
+    exact = ops.gemm_w8a16(x[rows], q, s, exact=True).double()
+    assert ((y[rows].double() - exact).abs() <= 2e-3 * ref.abs().amax(1, keepdim=True) + 1e-3).all()
+    full = x.cuda().float() @ (q.cuda().float() * s.cuda().float()[None])
+    err = (y.cuda().float() - full).abs()
+    assert bool((err <= 1e-2 * full.abs().amax(1, keepdim=True)).all()), float(err.max())
+    res = torch.randn(M, N, generator=gen).half()
+    yr = _run(x, q, s, residual=res)
+    # the partials are added in rank order: the residual run repeats the plain run bit for bit before the add
+    assert torch.equal(yr, ops.add_residual(y, res))
+
+
+@pytest.mark.parametrize("KNM", [(256, 4096, 2560), (192, 2560, 4000), (1088, 2816, 3400), (4096, 12288, 2304)])
+def test_persistent_tiles_in_waves(KNM):
+    """More 256 x 256 tiles than SMs, and no multiple of them: persistent CTAs take tiles i, i + G, ... and run
+    two to four of them back to back on the same rings, barriers and tensor memory (short and odd k-loops of 4, 3
+    and 17 k-blocks, a ragged last token tile, the fused QKV shape of LLaMA-7B); with and without the residual, and
+    twice in a row (the kernel is deterministic).  Every element against an fp32 matmul of the dequantized weights
+    run by torch on the GPU (checker only), sampled rows against the fp64 oracle."""
+    K, N, M = KNM
+    gen = torch.Generator().manual_seed(K + N + M)
+    q = torch.randint(-128, 128, (K, N), generator=gen, dtype=torch.int8)
+    s = (torch.rand(N, generator=gen) * 3e-4 + 1e-4).half()
+    x = torch.randn(M, K, generator=gen).half()
+    y = _run(x, q, s)
+    rows = torch.tensor(sorted({0, 1, 255, 256, 257, 511, 1023, 1024, M // 2, M - 257, M - 2, M - 1} & set(range(M))))
+    ref = ops.gemm_w8a16_fp32(x[rows], q, s)
+    assert ((y[rows].double() - ref).abs() <= 1e-2 * ref.abs().amax(1, keepdim=True)).all()
+    full = x.cuda().float() @ (q.cuda().float() * s.cuda().float()[None])
+    err = (y.cuda().float() - full).abs()
+    assert bool((err <= 1e-2 * full.abs().amax(1, keepdim=True)).all()), float(err.max())
+    del full, err
+    assert torch.equal(_run(x, q, s), y)
+    res = torch.randn(M, N, generator=gen).half()
+    yr = _run(x, q, s, residual=res)
+    assert torch.equal(yr, ops.add_residual(y, res))
