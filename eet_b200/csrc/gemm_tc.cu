@@ -405,7 +405,7 @@ struct Tc2Seg {
 };
 
 struct Tc2Work {
-    int KT, G, i, nseg, cluster_kb0, cluster_kb1, cluster_tile;
+    int KT, G, i, tile0, nseg, cluster_kb0, cluster_kb1, cluster_tile;
 
     __device__ Tc2Seg seg(int p) const
     {
@@ -417,7 +417,7 @@ struct Tc2Work {
             s.cluster = true;
             return s;
         }
-        s.tile = p * G + i;
+        s.tile = tile0 + p * G + i;
         s.kb0 = 0;
         s.kb1 = KT;
         s.cluster = false;
@@ -427,8 +427,10 @@ struct Tc2Work {
 
 __global__ void __launch_bounds__(kTc2Threads, 1)
 gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t* __restrict__ Bw, const __half* __restrict__ scale,
-                __half* __restrict__ C, const __half* __restrict__ residual, int M, int N, int K)
+                __half* __restrict__ C, const __half* __restrict__ residual, int M, int N, int K, int tile0, int tile_count)
 {
+    // This launch covers tiles [tile0, tile0 + tile_count) of the output, numbered row-major over (token tile,
+    // channel tile).
     extern __shared__ __align__(1024) uint8_t tc_dyn[];
     __shared__ Tc2Smem sm;
     uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(tc_dyn) + 1023) & ~(uintptr_t)1023);
@@ -445,17 +447,18 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t* __res
     wk.i = (int)blockIdx.x;
     wk.cluster_tile = -1;
     wk.cluster_kb0 = wk.cluster_kb1 = 0;
+    wk.tile0 = tile0;
     if (S > 1) {
-        // cluster mode: the cluster is the gridDim.z CTAs of tile (blockIdx.x, blockIdx.y)
-        wk.cluster_tile = (int)(blockIdx.y * tiles_n + blockIdx.x);
+        // cluster mode: the cluster is the gridDim.z CTAs of tile tile0 + blockIdx.x
+        wk.cluster_tile = tile0 + (int)blockIdx.x;
         wk.cluster_kb0 = (int)((long long)wk.KT * rank / S);
         wk.cluster_kb1 = (int)((long long)wk.KT * (rank + 1) / S);
         wk.nseg = 1;
     }
     else {
-        const int tiles = tiles_n * tiles_m;
-        wk.nseg = (tiles - wk.i + wk.G - 1) / wk.G;   // tiles i, i + G, ...
+        wk.nseg = (tile_count - wk.i + wk.G - 1) / wk.G;   // tiles tile0 + i, tile0 + i + G, ...
     }
+    (void)tiles_m;
     const int nseg = wk.nseg;
 
     pdl_launch_dependents();
@@ -703,7 +706,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t* __res
         const int tw = (warp - (grp ? 7 : 2)) * 32 + lane;   // 0..127 within the group
         const int lane_base = (warp & 3) * 32;
         const int ch = grp * 128 + lane_base + lane;          // this thread's channel of the tile
-        const int n0 = blockIdx.x * 256, m0 = blockIdx.y * 256;
+        const int n0 = (wk.cluster_tile % tiles_n) * 256, m0 = (wk.cluster_tile / tiles_n) * 256;
         uint8_t* red = base + kTc2StageBytes;
         // All CTAs of the cluster have completed their MMAs: their rings may be overwritten.
         cooperative_groups::this_cluster().sync();
@@ -849,6 +852,20 @@ static int tc2_max_clusters(int split)
     return cached[dev][split] > 0 ? cached[dev][split] : 0;
 }
 
+// Largest cluster size (4, 3, 2) over which the k-blocks of each of `tiles` tiles can be split: all clusters
+// resident at once, at least four k-blocks per CTA; 0 if none.  (Clusters of 8 were measured too: the all-to-all
+// of 7/8 of every accumulator costs more than the shorter k-loops save.)
+static int tc2_cluster_size(int tiles, int K)
+{
+    const int KT = K / kTile;
+    static const int sizes[3] = {4, 3, 2};
+    for (int i = 0; i < 3; ++i) {
+        const int sp = sizes[i];
+        if (KT / sp >= 4 && tiles <= tc2_max_clusters(sp)) return sp;
+    }
+    return 0;
+}
+
 // How the 256 x 256 kernel would run this shape: 0 = not at all, 1 = whole tiles on persistent CTAs, 2/3/4 = the
 // k-blocks of a tile split over a cluster of that size.  Whole tiles need most of the machine's worth of them
 // (120); below that the largest split is taken that puts at least 96 CTAs to work, whose clusters are all
@@ -864,16 +881,9 @@ int tc2_split(int M, int N, int K)
     const long long tiles = (long long)(N / 256) * ((M + 255) / 256);
     if (forced == 0) return tiles >= 120 ? 1 : 0;
     if (tiles >= 120) return 1;
-    const int KT = K / kTile;
-    static const int sizes[3] = {4, 3, 2};
-    for (int i = 0; i < 3; ++i) {
-        const int sp = sizes[i];
-        if (forced > 0 && sp != forced) continue;
-        // (clusters of 8 were measured too: the all-to-all of 7/8 of every accumulator costs more than the
-        // shorter k-loops save)
-        if (KT / sp >= 4 && tiles * sp >= 96 && tiles <= tc2_max_clusters(sp)) return sp;
-    }
-    return 0;
+    const int sp = tc2_cluster_size((int)tiles, K);
+    if (forced > 0) return (sp > 0 && K / kTile / forced >= 4 && tiles <= tc2_max_clusters(forced)) ? forced : 0;
+    return (sp > 1 && tiles * sp >= 96) ? sp : 0;
 }
 
 bool gemm_tc_supported(int M, int N, int K)
@@ -911,28 +921,41 @@ int launch_gemm_tc(const __half* A, const uint8_t* B, const __half* scale, __hal
             EET_CUDA(cudaFuncSetAttribute(gemm_tc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
             attr_set2[dev] = true;
         }
-        cudaLaunchConfig_t cfg = {};
-        if (split == 1) {
-            // one persistent CTA per SM, fewer when there are fewer tiles
-            const long long tiles = (long long)(N / 256) * ((M + 255) / 256);
-            cfg.gridDim = dim3((unsigned)(tiles < sm_count() ? tiles : sm_count()), 1, 1);
+        const int tiles = (N / 256) * ((M + 255) / 256);
+        auto launch = [&](int tile0, int count, int grid_x, int cluster) -> cudaError_t {
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3((unsigned)grid_x, 1, (unsigned)cluster);
+            cfg.blockDim = dim3(kTc2Threads, 1, 1);
+            cfg.dynamicSmemBytes = smem;
+            cfg.stream = stream;
+            cudaLaunchAttribute attr[2];
+            attr[0].id = cudaLaunchAttributeClusterDimension;
+            attr[0].val.clusterDim.x = 1;
+            attr[0].val.clusterDim.y = 1;
+            attr[0].val.clusterDim.z = (unsigned)cluster;
+            attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            attr[1].val.programmaticStreamSerializationAllowed = 1;
+            cfg.attrs = attr;
+            cfg.numAttrs = 2;
+            return cudaLaunchKernelEx(&cfg, gemm_tc2_kernel, map, B, scale, C, residual, M, N, K, tile0, count);
+        };
+        if (split > 1) {
+            EET_CUDA(launch(0, tiles, tiles, split));
+            return 0;
+        }
+        // Whole tiles on one persistent CTA per SM (fewer when there are fewer tiles).  When the last wave would
+        // be at most half full, its tiles go to a second launch that splits each over a cluster instead: a
+        // quarter or a third of the k-blocks per CTA rather than a full tile's worth on a fifth of the SMs.
+        const int G = tiles < sm_count() ? tiles : sm_count();
+        const int left = tiles % G;
+        const int left_split = (left > 0 && 2 * left <= G) ? tc2_cluster_size(left, K) : 0;
+        if (left_split > 1) {
+            EET_CUDA(launch(0, tiles - left, G, 1));
+            EET_CUDA(launch(tiles - left, left, left, left_split));
         }
         else {
-            cfg.gridDim = dim3(N / 256, (M + 255) / 256, split);
+            EET_CUDA(launch(0, tiles, G, 1));
         }
-        cfg.blockDim = dim3(kTc2Threads, 1, 1);
-        cfg.dynamicSmemBytes = smem;
-        cfg.stream = stream;
-        cudaLaunchAttribute attr[2];
-        attr[0].id = cudaLaunchAttributeClusterDimension;
-        attr[0].val.clusterDim.x = 1;
-        attr[0].val.clusterDim.y = 1;
-        attr[0].val.clusterDim.z = split;
-        attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attr[1].val.programmaticStreamSerializationAllowed = 1;
-        cfg.attrs = attr;
-        cfg.numAttrs = 2;
-        EET_CUDA(cudaLaunchKernelEx(&cfg, gemm_tc2_kernel, map, B, scale, C, residual, M, N, K));
         return 0;
     }
     if (bn == 256) return launch_tc<256>(map, B, scale, C, residual, M, N, K, stream);
