@@ -345,9 +345,10 @@ def cpu_decode_sample(steps, warmup=1, budget_s=15.0, threads=None):
 
 def profile_kernels():
     """A handful of launches for profiler captures of the tensor-core kernels (`--profile-kernels`): the stream-K
-    kernel at M = 32 and M = 256 on K=8192, N=22016, the 256 x 256 tile kernel at M = 4096 on K=4096, N=11008,
-    and the prefill attention at B=8, H=32, S=512.  Every working set exceeds L2; nothing is timed or printed
-    but the device status."""
+    kernel at M = 32 and M = 256 on K=8192, N=22016, the 256 x 256 tile kernel at M = 4096 on K=4096, N=11008
+    (persistent CTAs) and at M = 1024 on K=11008, N=4096 (split-K over clusters of two), the stream-K kernel on
+    a LLaMA-7B shape (K=N=4096, M = 256), and the prefill attention at B=8, H=32, S=512.  The working sets of the
+    first three GEMMs and of the attention exceed L2; nothing is timed or printed but the device status."""
     from eet_b200 import EET, _lib
     from eet_b200._lib import check, lib
     dev = torch.device("cuda", 0)
@@ -364,6 +365,8 @@ def profile_kernels():
     gemm(8192, 22016, 32)
     gemm(8192, 22016, 256)
     gemm(4096, 11008, 4096)
+    gemm(11008, 4096, 1024)
+    gemm(4096, 4096, 256)
     B, H, S, D, T = 8, 32, 512, 128, 640
     q = torch.randn(B, H, S, D, device=dev).half()
     k = torch.randn(B, H, T, D, device=dev).half()

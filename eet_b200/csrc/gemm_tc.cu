@@ -650,7 +650,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t* __res
             if (!ok) break;
 
             // ---- end of the segment: every epilogue warp gets here (the waits are bounded); the OR-reducing
-            // barrier gives all 256 epilogue threads the same verdict, whoever saw the abort flag first ----
+            // barrier gives all 256 epilogue threads the same answer, whoever saw the abort flag first ----
             tc_wait(&sm.accum, (uint32_t)(p & 1), &sm.abort);
             if (epi_bar_or(sm.abort != 0)) {
                 ok = false;

@@ -105,8 +105,9 @@ size_t eet_gemm_w8a16_workspace_bytes(int M, int N, int K);
  *   residual  device fp16 [M][N] for epilogue 1, else NULL (may alias C)
  * M may be any value >= 0; K and N must be multiples of 64; pointers 16-byte aligned.
  * Kernels: M <= 16 TMA-staged skinny kernel; 16 < M <= 512 (N % 128 == 0) stream-K tcgen05 kernel; above
- * that tcgen05 kernels with 256 x 256 or 128 x 256 output tiles that need no scratch; shapes none of them
- * takes fall back to the skinny kernel in groups of 128 rows.
+ * that - and from M = 65 on for shapes (N % 256 == 0) whose 256 x 256 tiles, whole or with their k-blocks split
+ * over clusters of 2-4 CTAs, can occupy most of the GPU - tcgen05 kernels with 256 x 256 or 128 x 256 output
+ * tiles that need no scratch; shapes none of them takes fall back to the skinny kernel in groups of 128 rows.
  */
 int eet_gemm_w8a16(const void* A, const void* packedB, const void* scale, void* C, int M, int N, int K,
                    const void* residual, int epilogue, void* ws, size_t ws_bytes, void* stream);

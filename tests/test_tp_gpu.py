@@ -64,7 +64,7 @@ def _worker(rank, world, port, q, small, batch=8):
         everyone = [torch.empty_like(mine) for _ in range(world)]
         dist.all_gather(everyone, mine)
         assert all(torch.equal(e, mine) for e in everyone), "ranks disagree on the decode logits"
-        verdict = [None]
+        outcome = [None]
         if rank == 0:
             try:
                 lm = OracleLM(sd, cfg, max_len=T, batch=B, lm_head_int8=head_int8)
@@ -84,10 +84,10 @@ def _worker(rank, world, port, q, small, batch=8):
                         assert torch.equal(tok[clear], logits.argmax(-1)[clear]), f"{name}: generated token {t}"
                         logits = lm2(tok.view(B, 1), False)[:, -1]
             except AssertionError as e:
-                verdict[0] = f"rank 0 against the oracle: {e}"
+                outcome[0] = f"rank 0 against the oracle: {e}"
         # everybody learns the outcome, so that no rank is left waiting for one that has already given up
-        dist.broadcast_object_list(verdict, src=0)
-        assert verdict[0] is None, verdict[0]
+        dist.broadcast_object_list(outcome, src=0)
+        assert outcome[0] is None, outcome[0]
         dist.barrier()
         q.put((rank, "ok"))
         # graphs that captured NCCL kernels must go before the communicator does
