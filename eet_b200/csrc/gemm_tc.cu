@@ -337,8 +337,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t* __rest
 // Two ways to spread the tiles over the SMs:
 //
 // (a) Persistent CTAs (gridDim.z == 1), one per SM (fewer when there are fewer tiles): CTA i takes tiles i, i + G,
-//     i + 2G, ... so that the CTAs of a wave walk the k-blocks in step - CTAs that read the same activation or
-//     weight tile at the same time are served together by the L2.  The rings and all phase counters run on
+//     i + 2G, ... so that the CTAs of a wave walk the k-blocks in step: 16 CTAs want the same activation or
+//     weight tile at about the same time (measured: out of step the k-loop runs 1.3x slower).  The rings and all
+//     phase counters run on
 //     across tiles: while the transform warps are busy with a tile's epilogue, the producers already fetch the
 //     next tile's first k-blocks.  The epilogue's fp16 staging tiles live in the fp16 weight ring, which is idle
 //     exactly then (all MMAs of the tile have completed, the next conversions come after).
@@ -351,7 +352,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t* __rest
 //     costs what the shorter wave saves.
 //
 // (b) Split-K over a thread-block cluster (gridDim.z = cluster size S = 2, 3 or 4) for shapes with fewer tiles
-//     than SMs: the S CTAs of a cluster share one output tile (blockIdx.x, blockIdx.y) and each walks 1/S of the
+//     than SMs: the S CTAs of a cluster share one output tile (tile0 + blockIdx.x) and each walks 1/S of the
 //     k-blocks.  The partial accumulators meet through distributed shared memory, never through global memory:
 //     the tile's eight 32-token blocks are dealt out to the ranks (block b belongs to rank b % S), every CTA
 //     stores its partial of a foreign block into the owner's shared memory (the operand rings are idle by then;
