@@ -10,7 +10,7 @@
 // of K) of one 128-channel strip; the units are cut into as many equal, contiguous ranges as CTAs fit on
 // the GPU (two per SM), so all SMs stream weights whatever N is, and a range that crosses a strip boundary
 // simply ends one accumulation and starts the next.  Per CTA:
-//   warp 0      weight producer: the int8 tiles of a unit (two 1-D bulk copies of up to 8 KiB), ring 3-4 deep;
+//   warp 0      weight producer: the int8 tiles of a unit (two 1-D bulk copies of up to 8 KiB), ring 3-5 deep;
 //   warp 10     activation producer: the BN x 64 tiles of the unit's k-blocks (2-D tensor map, 128-byte
 //               swizzle, rows past M read as zeros), ring 3-4 deep - L2 hits, but as slow as DRAM while the
 //               weights stream;
@@ -39,9 +39,11 @@ constexpr int kMidThreads = 352;
 constexpr int kMidUnitK = 2;                         // k-blocks per unit
 constexpr int kMidWStage = kMidUnitK * kTcW8Bytes;   // 16 KiB: [channel half][k-block][64 x 64 bytes]
 constexpr int kMidACols = kMidUnitK * 32;            // TMEM columns of one fp16 weight buffer: 64 k as half2 each
-constexpr int kMidNWMax = 4, kMidNXMax = 4, kMidNHMax = 4;
+constexpr int kMidNWMax = 6, kMidNXMax = 4, kMidNHMax = 4;
 
-__host__ __device__ constexpr int mid_nw(int bn) { return bn == 64 ? 3 : 4; }
+// (128-token tiles: the kernel alone runs as fast with four weight stages, but a call - this kernel followed by the
+// finalize launch - measured 0.5-2.4 us shorter with five)
+__host__ __device__ constexpr int mid_nw(int bn) { return bn == 64 ? 3 : (bn == 128 ? 5 : 4); }
 __host__ __device__ constexpr int mid_nx(int bn) { return bn == 32 ? 4 : (bn == 256 ? 2 : 3); }
 // accumulator buffers: two (the epilogue of a strip overlaps the next strip's MMAs) while they fit beside
 // the fp16 weight buffers; one for 256-token tiles
