@@ -237,18 +237,22 @@ def repack_reference_weights(ref_packed):
 # ---------------------------------------------------------------------------------------------------
 # GEMM helper shared by the ops
 # ---------------------------------------------------------------------------------------------------
-def gemm_w8a16(x, packed_w, scale, out=None, residual=None):
-    """out[M, N] = x[M, K] @ dequant(packed_w) (+ residual).  x fp16 CUDA contiguous; packed_w int8 [K, N]
+def gemm_w8a16(x, packed_w, scale, out=None, residual=None, gate=None):
+    """out[M, N] = x[M, K] @ dequant(packed_w) (+ residual), or gated_silu(gate, x @ dequant(packed_w)) with `gate`
+    (the gate projection of a gated FFN; may be `out` itself).  x fp16 CUDA contiguous; packed_w int8 [K, N]
     W8T64 bytes; scale fp16 [N].  The functional form of fastertransformer::gemm_fp16_int_bias_act as the
     ops call it (csrc/op/llama_mmha.cpp:319-331)."""
     K, N = packed_w.shape
     M = x.numel() // K
     if out is None:
         out = torch.empty((M, N), dtype=torch.float16, device=x.device)
+    if gate is not None and residual is not None:
+        raise RuntimeError("gemm_w8a16: residual and gate exclude each other")
+    second, epilogue = (gate, 2) if gate is not None else (residual, 1 if residual is not None else 0)
     ws_bytes = lib.eet_gemm_w8a16_workspace_bytes(M, N, K)
     ws = _pool.gemm_workspace(ws_bytes, x.device)
     check(lib.eet_gemm_w8a16(x.data_ptr(), packed_w.data_ptr(), scale.data_ptr(), out.data_ptr(), M, N, K,
-                             _ptr(residual), 1 if residual is not None else 0, ws.data_ptr(), ws.numel(), _stream()))
+                             _ptr(second), epilogue, ws.data_ptr(), ws.numel(), _stream()))
     return out
 
 
@@ -696,10 +700,14 @@ class GatedFeedForwardNetworkInt8:
                 check(lib.eet_swiglu_finalize(gs.data_ptr(), self.s0.data_ptr(), us.data_ptr(), self.s1.data_ptr(),
                                               act.data_ptr(), M, self.d_ff, _stream()))
             else:
-                lin = _pool.get("ffn_inner_linear", cap * self.d_ff, torch.float16, d.device)[: M * self.d_ff].view(M, self.d_ff)
                 _linear(xn, self.w0, self.s0, act)
-                _linear(xn, self.w1, self.s1, lin)
-                check(lib.eet_swiglu(act.data_ptr(), lin.data_ptr(), M, self.d_ff, _stream()))
+                if self.w1.dtype == torch.int8:
+                    # the gated activation runs in the up projection's epilogue, on the gate values already in `act`
+                    gemm_w8a16(xn, self.w1, self.s1, out=act, gate=act)
+                else:
+                    lin = _pool.get("ffn_inner_linear", cap * self.d_ff, torch.float16, d.device)[: M * self.d_ff].view(M, self.d_ff)
+                    _linear(xn, self.w1, self.s1, lin)
+                    check(lib.eet_swiglu(act.data_ptr(), lin.data_ptr(), M, self.d_ff, _stream()))
             if deferred and add_residual:
                 peer = None
                 if d.tp is not None and d.tp.size > 1:

@@ -209,9 +209,11 @@ int eet_gemm_w8a16(const void* A, const void* packedB, const void* scale, void* 
     if (check_gemm("eet_gemm_w8a16", A, packedB, M, N, K)) return 1;
     if (M == 0) return 0;
     EET_CHECK(scale && C && aligned16(C) && aligned16(scale), "eet_gemm_w8a16: scale and C must be 16-byte aligned buffers");
-    EET_CHECK(epilogue == 0 || epilogue == 1, "eet_gemm_w8a16: unknown epilogue %d", epilogue);
-    EET_CHECK(epilogue != 1 || residual != nullptr, "eet_gemm_w8a16: epilogue 1 needs a residual");
-    const __half* res = epilogue == 1 ? (const __half*)residual : nullptr;
+    EET_CHECK(epilogue >= 0 && epilogue <= 2, "eet_gemm_w8a16: unknown epilogue %d", epilogue);
+    EET_CHECK(epilogue == 0 || (residual != nullptr && aligned16(residual)),
+              "eet_gemm_w8a16: epilogues 1 and 2 need a 16-byte aligned second operand");
+    const __half* res = epilogue != 0 ? (const __half*)residual : nullptr;
+    const int gate = epilogue == 2 ? 1 : 0;
     // Above 64 tokens a shape that the 256 x 256 kernel can spread over the machine (plain tiles or split-K
     // clusters) goes there: one launch, epilogue fused, no fp32 scratch.
     const bool tiles_first = M > 64 && gemm_tc_supported(M, N, K) && tc2_split(M, N, K) > 0;
@@ -227,12 +229,12 @@ int eet_gemm_w8a16(const void* A, const void* packedB, const void* scale, void* 
         a.N = N;
         a.K = K;
         if (int rc = launch_gemm_mid(a, (cudaStream_t)stream)) return rc;
-        return launch_finalize((float*)ws, (const __half*)scale, res, (__half*)C, M, N, (cudaStream_t)stream);
+        return launch_finalize((float*)ws, (const __half*)scale, res, (__half*)C, M, N, (cudaStream_t)stream, gate);
     }
     if (gemm_tc_supported(M, N, K)) {
         // prefill regime: tcgen05 tensor-core kernel, epilogue fused, no scratch
-        return launch_gemm_tc((const __half*)A, (const uint8_t*)packedB, (const __half*)scale, (__half*)C, res, M, N, K,
-                              (cudaStream_t)stream);
+        return launch_gemm_tc((const __half*)A, (const uint8_t*)packedB, (const __half*)scale, (__half*)C, res, gate, M, N,
+                              K, (cudaStream_t)stream);
     }
     EET_CHECK(ws && aligned16(ws) && ws_bytes >= eet_gemm_w8a16_workspace_bytes(M, N, K),
               "eet_gemm_w8a16: workspace of %zu bytes is smaller than the %zu needed", ws_bytes,
@@ -248,7 +250,7 @@ int eet_gemm_w8a16(const void* A, const void* packedB, const void* scale, void* 
         a.K = K;
         if (int rc = launch_gemm_skinny(a, (cudaStream_t)stream)) return rc;
         if (int rc = launch_finalize((float*)ws, (const __half*)scale, res ? res + (size_t)r0 * N : nullptr,
-                                     (__half*)C + (size_t)r0 * N, rows, N, (cudaStream_t)stream))
+                                     (__half*)C + (size_t)r0 * N, rows, N, (cudaStream_t)stream, gate))
             return rc;
     }
     return 0;

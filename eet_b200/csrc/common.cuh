@@ -137,6 +137,16 @@ __device__ __forceinline__ void bulk_g2s_stream(void* smem_dst, const void* gmem
         : "memory");
 }
 
+// gate <- up * gate / (1 + exp(-gate)) with the reference's mix of precisions: exp in fp32 rounded to
+// fp16, the multiply, add and divide in fp16 (gated_silu<half>, csrc/core/activation_kernel.cu:106-124).
+__device__ __forceinline__ __half2 gated_silu2(__half2 g, __half2 u)
+{
+    const float2 gf = __half22float2(g);
+    const __half2 e = __floats2half2_rn(expf(-gf.x), expf(-gf.y));
+    const __half2 one = __floats2half2_rn(1.f, 1.f);
+    return __h2div(__hmul2(u, g), __hadd2(one, e));
+}
+
 // Four biased bytes (value + 128 each) -> four fp16 values, as two half2 registers {b0,b1} and {b2,b3}.
 // Placing a byte under the exponent pattern 0x64 yields the fp16 number 1024 + byte; subtracting 1152
 // gives byte - 128 exactly.

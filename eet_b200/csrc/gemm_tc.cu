@@ -144,7 +144,7 @@ constexpr int kEpiStageHalves = 32 * 128;
 
 template<int kBarId = 1>
 __device__ __forceinline__ void epilogue_block(const uint32_t (&v)[32], float sc, __half* stage, int channel, int tw,
-                                               __half* C, const __half* residual, int m_first, int M, int N,
+                                               __half* C, const __half* residual, int gate, int m_first, int M, int N,
                                                int n_first)
 {
 #pragma unroll
@@ -167,8 +167,15 @@ __device__ __forceinline__ void epilogue_block(const uint32_t (&v)[32], float sc
             if (residual != nullptr) {
                 __half2* oh = reinterpret_cast<__half2*>(&o);
                 const __half2* rh = reinterpret_cast<const __half2*>(&res[i]);
+                if (gate) {
+                    // the second operand is the gate projection: this GEMM is the up projection of a gated FFN
 #pragma unroll
-                for (int e = 0; e < 4; ++e) oh[e] = __hadd2(oh[e], rh[e]);
+                    for (int e = 0; e < 4; ++e) oh[e] = gated_silu2(rh[e], oh[e]);
+                }
+                else {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) oh[e] = __hadd2(oh[e], rh[e]);
+                }
             }
             *reinterpret_cast<uint4*>(C + (size_t)(m_first + row) * N + n_first + ch8 * 8) = o;
         }
@@ -178,7 +185,7 @@ __device__ __forceinline__ void epilogue_block(const uint32_t (&v)[32], float sc
 template<int BN>
 __global__ void __launch_bounds__(kTcThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t* __restrict__ Bw, const __half* __restrict__ scale,
-               __half* __restrict__ C, const __half* __restrict__ residual, int M, int N, int K)
+               __half* __restrict__ C, const __half* __restrict__ residual, int gate, int M, int N, int K)
 {
     extern __shared__ __align__(1024) uint8_t tc_dyn[];
     __shared__ TcSmem sm;
@@ -310,7 +317,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t* __rest
                 uint32_t v[32];
                 tmem_ld32(tmem + ((uint32_t)lane_base << 16) + (uint32_t)c0, v);
                 epilogue_block(v, sc, stage + ((c0 >> 5) & 1) * kEpiStageHalves, lane_base + lane, tw, C, residual,
-                               m0 + c0, M, N, n0);
+                               gate, m0 + c0, M, N, n0);
             }
         }
     }
@@ -428,7 +435,8 @@ struct Tc2Work {
 
 __global__ void __launch_bounds__(kTc2Threads, 1)
 gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t* __restrict__ Bw, const __half* __restrict__ scale,
-                __half* __restrict__ C, const __half* __restrict__ residual, int M, int N, int K, int tile0, int tile_count)
+                __half* __restrict__ C, const __half* __restrict__ residual, int gate, int M, int N, int K, int tile0,
+                int tile_count)
 {
     // This launch covers tiles [tile0, tile0 + tile_count) of the output, numbered row-major over (token tile,
     // channel tile).
@@ -675,12 +683,12 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t* __res
                     uint32_t v[32];
                     tmem_ld32(tmem + ((uint32_t)lane_base << 16) + (uint32_t)(grp * 256 + c0), v);
                     if (grp == 0) {
-                        epilogue_block<1>(v, sc, stage + (blk & 1) * kEpiStageHalves, lane_base + lane, tw, C, residual, m0 + c0,
-                                          M, N, n0);
+                        epilogue_block<1>(v, sc, stage + (blk & 1) * kEpiStageHalves, lane_base + lane, tw, C, residual, gate,
+                                          m0 + c0, M, N, n0);
                     }
                     else {
-                        epilogue_block<2>(v, sc, stage + (blk & 1) * kEpiStageHalves, lane_base + lane, tw, C, residual, m0 + c0,
-                                          M, N, n0 + 128);
+                        epilogue_block<2>(v, sc, stage + (blk & 1) * kEpiStageHalves, lane_base + lane, tw, C, residual, gate,
+                                          m0 + c0, M, N, n0 + 128);
                     }
                 }
                 // The staging tiles lie in this group's own part of the fp16 weight ring: its next conversions
@@ -758,12 +766,12 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_x, const uint8_t* __res
                     }
                 }
                 if (grp == 0) {
-                    epilogue_block<1>(v, sc, stage + (blk & 1) * kEpiStageHalves, lane_base + lane, tw, C, residual, m0 + c0, M, N,
-                                      n0);
+                    epilogue_block<1>(v, sc, stage + (blk & 1) * kEpiStageHalves, lane_base + lane, tw, C, residual, gate, m0 + c0, M,
+                                      N, n0);
                 }
                 else {
-                    epilogue_block<2>(v, sc, stage + (blk & 1) * kEpiStageHalves, lane_base + lane, tw, C, residual, m0 + c0, M, N,
-                                      n0 + 128);
+                    epilogue_block<2>(v, sc, stage + (blk & 1) * kEpiStageHalves, lane_base + lane, tw, C, residual, gate, m0 + c0, M,
+                                      N, n0 + 128);
                 }
             }
         }
@@ -795,8 +803,8 @@ EncodeTiledFn encode_tiled_fn()
 }
 
 template<int BN>
-int launch_tc(const CUtensorMap& map, const uint8_t* B, const __half* scale, __half* C, const __half* residual, int M,
-              int N, int K, cudaStream_t stream)
+int launch_tc(const CUtensorMap& map, const uint8_t* B, const __half* scale, __half* C, const __half* residual, int gate,
+              int M, int N, int K, cudaStream_t stream)
 {
     static bool attr_set[64] = {};
     int dev = 0;
@@ -808,7 +816,7 @@ int launch_tc(const CUtensorMap& map, const uint8_t* B, const __half* scale, __h
         attr_set[dev] = true;
     }
     dim3 grid(N / 128, (M + BN - 1) / BN);
-    gemm_tc_kernel<BN><<<grid, kTcThreads, smem, stream>>>(map, B, scale, C, residual, M, N, K);
+    gemm_tc_kernel<BN><<<grid, kTcThreads, smem, stream>>>(map, B, scale, C, residual, gate, M, N, K);
     EET_LAUNCH_CHECK();
     return 0;
 }
@@ -892,8 +900,8 @@ bool gemm_tc_supported(int M, int N, int K)
     return M >= kTcMinM && N % 128 == 0 && K % 64 == 0;
 }
 
-int launch_gemm_tc(const __half* A, const uint8_t* B, const __half* scale, __half* C, const __half* residual, int M,
-                   int N, int K, cudaStream_t stream)
+int launch_gemm_tc(const __half* A, const uint8_t* B, const __half* scale, __half* C, const __half* residual, int gate,
+                   int M, int N, int K, cudaStream_t stream)
 {
     EET_CHECK(gemm_tc_supported(M, N, K), "tensor-core GEMM: needs M >= 65, N %% 128 == 0, K %% 64 == 0");
     EncodeTiledFn encode = encode_tiled_fn();
@@ -938,7 +946,7 @@ int launch_gemm_tc(const __half* A, const uint8_t* B, const __half* scale, __hal
             attr[1].val.programmaticStreamSerializationAllowed = 1;
             cfg.attrs = attr;
             cfg.numAttrs = 2;
-            return cudaLaunchKernelEx(&cfg, gemm_tc2_kernel, map, B, scale, C, residual, M, N, K, tile0, count);
+            return cudaLaunchKernelEx(&cfg, gemm_tc2_kernel, map, B, scale, C, residual, gate, M, N, K, tile0, count);
         };
         if (split > 1) {
             EET_CUDA(launch(0, tiles, tiles, split));
@@ -959,9 +967,9 @@ int launch_gemm_tc(const __half* A, const uint8_t* B, const __half* scale, __hal
         }
         return 0;
     }
-    if (bn == 256) return launch_tc<256>(map, B, scale, C, residual, M, N, K, stream);
-    if (bn == 128) return launch_tc<128>(map, B, scale, C, residual, M, N, K, stream);
-    return launch_tc<64>(map, B, scale, C, residual, M, N, K, stream);
+    if (bn == 256) return launch_tc<256>(map, B, scale, C, residual, gate, M, N, K, stream);
+    if (bn == 128) return launch_tc<128>(map, B, scale, C, residual, gate, M, N, K, stream);
+    return launch_tc<64>(map, B, scale, C, residual, gate, M, N, K, stream);
 }
 
 }  // namespace eet

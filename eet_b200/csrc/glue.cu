@@ -91,7 +91,7 @@ __device__ __forceinline__ void load_sums8(float* p, float (&v)[8])
 }
 
 // 8 outputs: fp16(sum * scale) (+ residual in fp16)
-__device__ __forceinline__ uint4 finalize8(const float (&v)[8], const uint4& scale, const uint4* residual)
+__device__ __forceinline__ uint4 finalize8(const float (&v)[8], const uint4& scale, const uint4* residual, bool gate = false)
 {
     const __half2* sh = reinterpret_cast<const __half2*>(&scale);
     uint4 o;
@@ -103,16 +103,22 @@ __device__ __forceinline__ uint4 finalize8(const float (&v)[8], const uint4& sca
     }
     if (residual != nullptr) {
         const __half2* rh = reinterpret_cast<const __half2*>(residual);
+        if (gate) {
 #pragma unroll
-        for (int e = 0; e < 4; ++e) oh[e] = __hadd2(oh[e], rh[e]);
+            for (int e = 0; e < 4; ++e) oh[e] = gated_silu2(rh[e], oh[e]);
+        }
+        else {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) oh[e] = __hadd2(oh[e], rh[e]);
+        }
     }
     return o;
 }
 
-// C = fp16(sums * scale) (+ residual); sums <- 0.
+// C = fp16(sums * scale) (+ residual, or gated_silu(residual, .) with gate set); sums <- 0.
 __global__ void __launch_bounds__(256)
 finalize_kernel(float* __restrict__ sums, const __half* __restrict__ scale, const __half* __restrict__ residual,
-                __half* __restrict__ C, int N, size_t nvec)
+                __half* __restrict__ C, int N, size_t nvec, int gate)
 {
     pdl_launch_dependents();
     pdl_wait();
@@ -124,7 +130,7 @@ finalize_kernel(float* __restrict__ sums, const __half* __restrict__ scale, cons
     const uint4 sc = *reinterpret_cast<const uint4*>(scale + col);
     uint4 r;
     if (residual != nullptr) r = reinterpret_cast<const uint4*>(residual)[i];
-    reinterpret_cast<uint4*>(C)[i] = finalize8(v, sc, residual ? &r : nullptr);
+    reinterpret_cast<uint4*>(C)[i] = finalize8(v, sc, residual ? &r : nullptr, gate != 0);
 }
 
 // Row kernel at the head of an attention or FFN block during decode.  With sums != null it first finishes
@@ -353,15 +359,7 @@ rmsnorm_finalize_tp_kernel(TpPeers peers, float* __restrict__ local_sums, int* _
     }
 }
 
-// gate <- up * gate / (1 + exp(-gate)) with the reference's mix of precisions: exp in fp32 rounded to
-// fp16, the multiply, add and divide in fp16 (gated_silu<half>, csrc/core/activation_kernel.cu:106-124).
-__device__ __forceinline__ __half2 gated_silu2(__half2 g, __half2 u)
-{
-    const float2 gf = __half22float2(g);
-    const __half2 e = __floats2half2_rn(expf(-gf.x), expf(-gf.y));
-    const __half2 one = __floats2half2_rn(1.f, 1.f);
-    return __h2div(__hmul2(u, g), __hadd2(one, e));
-}
+// (gated_silu2, the reference's gated SiLU on half2, lives in common.cuh: the GEMM epilogues use it too)
 
 __global__ void __launch_bounds__(256)
 swiglu_kernel(__half* __restrict__ gate, const __half* __restrict__ up, size_t nvec)
@@ -705,13 +703,13 @@ int launch_rmsnorm(const __half* x, const __half* gamma, __half* y, int M, int n
 }
 
 int launch_finalize(float* sums, const __half* scale, const __half* residual, __half* C, int M, int N,
-                    cudaStream_t stream)
+                    cudaStream_t stream, int gate)
 {
     EET_CHECK(N % 8 == 0, "finalize: N must be a multiple of 8");
     const size_t nvec = (size_t)M * N / 8;
     if (nvec == 0) return 0;
     EET_CUDA(launch_pdl(finalize_kernel, dim3((unsigned)((nvec + 255) / 256)), dim3(256), 0, stream, sums, scale,
-                        residual, C, N, nvec));
+                        residual, C, N, nvec, gate));
     return 0;
 }
 

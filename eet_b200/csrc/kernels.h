@@ -31,8 +31,8 @@ int launch_gemm_skinny(const GemmArgs& a, cudaStream_t stream);
 // gemm_tc.cu (tcgen05 / TMEM)
 bool gemm_tc_supported(int M, int N, int K);
 int tc2_split(int M, int N, int K);  // 0: the 256 x 256 kernel does not take this shape; else its split-K cluster size
-int launch_gemm_tc(const __half* A, const uint8_t* B, const __half* scale, __half* C, const __half* residual, int M,
-                   int N, int K, cudaStream_t stream);
+int launch_gemm_tc(const __half* A, const uint8_t* B, const __half* scale, __half* C, const __half* residual, int gate,
+                   int M, int N, int K, cudaStream_t stream);
 
 // gemm_mid.cu (stream-K tcgen05, fp32 sums like the skinny kernel)
 constexpr int kMidMaxM = 512;
@@ -46,7 +46,7 @@ int gemm_w8a16_noalloc(const __half* A, const uint8_t* B, const __half* scale, _
 // glue.cu
 int launch_rmsnorm(const __half* x, const __half* gamma, __half* y, int M, int n, float eps, cudaStream_t stream);
 int launch_finalize(float* sums, const __half* scale, const __half* residual, __half* C, int M, int N,
-                    cudaStream_t stream);
+                    cudaStream_t stream, int gate = 0);   // gate: C = gated_silu(residual, fp16(sums * scale))
 int launch_rmsnorm_finalize(float* sums, const __half* scale, const __half* residual, __half* h_out,
                             const __half* gamma, __half* xn_out, int M, int n, float eps, cudaStream_t stream);
 int launch_rmsnorm_finalize_tp(float* local_sums, void* const* peer_inbox, int world, int rank, int which, int* epochs,

@@ -101,8 +101,11 @@ size_t eet_gemm_w8a16_workspace_bytes(int M, int N, int K);
  *           fpA_intB_gemm/fpA_intB_gemm_template.h:545-558) as called from
  *           csrc/op/llama_mmha.cpp:313-337,428-447 and csrc/op/gated_ffn_int8.cpp:253-326.
  *   epilogue  0: C = A.B;  1: C = fp16(A.B) + residual in fp16, the add_input kernel that follows the
- *             projection GEMMs in the reference (csrc/core/add_bias.cu:22-28) fused in.
- *   residual  device fp16 [M][N] for epilogue 1, else NULL (may alias C)
+ *             projection GEMMs in the reference (csrc/core/add_bias.cu:22-28) fused in;  2: C =
+ *             gated_silu(residual, fp16(A.B)), i.e. this GEMM is the up projection of a gated FFN and `residual`
+ *             holds the gate projection: the reference's gated_act kernel (csrc/core/activation_kernel.cu:106-124,
+ *             called from csrc/op/gated_ffn_int8.cpp:290-301) fused in, with its mix of fp32 and fp16 arithmetic.
+ *   residual  device fp16 [M][N] for epilogues 1 and 2, else NULL (may alias C)
  * M may be any value >= 0; K and N must be multiples of 64; pointers 16-byte aligned.
  * Kernels: M <= 16 TMA-staged skinny kernel; 16 < M <= 512 (N % 128 == 0) stream-K tcgen05 kernel; above
  * that - and from M = 65 on for shapes (N % 256 == 0) whose 256 x 256 tiles, whole or with their k-blocks split

@@ -309,3 +309,35 @@ def test_persistent_tiles_in_waves(KNM):
     res = torch.randn(M, N, generator=gen).half()
     yr = _run(x, q, s, residual=res)
     assert torch.equal(yr, ops.add_residual(y, res))
+
+
+@pytest.mark.parametrize("KNM", [(256, 384, 8), (256, 384, 100), (1024, 640, 1000), (4096, 4096, 512), (256, 4096, 2560),
+                                 (1088, 2816, 3400)])
+def test_gated_activation_epilogue(KNM):
+    """Epilogue 2: the GEMM is the up projection of a gated FFN and applies gated_silu(gate, .) to its own output,
+    in every kernel regime (skinny and stream-K kernels through the finalize launch, the 128 x 256 and 256 x 256
+    tensor-core kernels - persistent, cluster split, second launch for the last wave - in their epilogues), in
+    place (the output buffer holds the gate values) and out of place.  Expected: the oracle's gated_silu
+    (activation_kernel.cu:106-124) of the gate and of this library's plain GEMM output."""
+    from eet_b200 import EET, _lib
+    K, N, M = KNM
+    gen = torch.Generator().manual_seed(K + N + M)
+    q = torch.randint(-128, 128, (K, N), generator=gen, dtype=torch.int8)
+    s = (torch.rand(N, generator=gen) * 3e-4 + 1e-4).half()
+    x = torch.randn(M, K, generator=gen).half()
+    gate = (torch.randn(M, N, generator=gen) * 2).half()
+    packed = EET.preprocess_weights(q).cuda()
+    xc, sc = x.cuda(), s.cuda()
+    up = EET.gemm_w8a16(xc, packed, sc)
+    want = ops.gated_silu(gate, up.cpu())
+    got = EET.gemm_w8a16(xc, packed, sc, gate=gate.cuda())
+    buf = gate.cuda().clone()
+    got_inplace = EET.gemm_w8a16(xc, packed, sc, out=buf, gate=buf)
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0
+    # (the kernels that sum with atomics may round `up` differently in the last fp16 bit from run to run, and the
+    # device's expf may differ from the host's in the last bit before its rounding to fp16)
+    tol = dict(rtol=4e-3, atol=4e-3)
+    assert torch.allclose(got.cpu().float(), want.float(), **tol)
+    assert torch.allclose(got_inplace.cpu().float(), want.float(), **tol)
+    assert got_inplace.data_ptr() == buf.data_ptr()
