@@ -237,7 +237,10 @@ __device__ __forceinline__ uint4 ld_volatile_u4(const void* p)
 // One row is split over the CTAs of a thread-block cluster (up to 8): the peer stores of a row leave from
 // up to 8 SMs instead of one (what one SM can push over NVLink per microsecond bounded the exchange at 4 and 8
 // ranks), and the row's sum of squares meets through distributed shared memory.  One 8-float vector per thread.
-__global__ void __launch_bounds__(1024)
+// kMaxThreads = 256 (every hidden size up to 16384 with a cluster of 8) leaves the registers for polling all peers
+// at once; 1024 is the fallback for rows that a smaller cluster has to cover.
+template<int kMaxThreads>
+__global__ void __launch_bounds__(kMaxThreads)
 rmsnorm_finalize_tp_kernel(TpPeers peers, float* __restrict__ local_sums, int* __restrict__ epochs,
                            const __half* __restrict__ scale, const __half* __restrict__ residual,
                            __half* __restrict__ h_out, const __half* __restrict__ gamma, __half* __restrict__ xn_out,
@@ -289,36 +292,84 @@ rmsnorm_finalize_tp_kernel(TpPeers peers, float* __restrict__ local_sums, int* _
         }
     }
 
-    // ---- collect: poll the local inbox until every peer's pairs carry this epoch, add in rank order ----
+    // ---- collect: poll the local inbox until every peer's packets carry this epoch, add in rank order ----
     float v[8];
 #pragma unroll
     for (int e = 0; e < 8; ++e) v[e] = 0.f;
+    if (kMaxThreads <= 256) {
+        // All pending peers are polled in the same round trip: a poll is a load from this GPU's memory (about a
+        // microsecond under load), and seven of them one after the other used to be most of the exchange.
+        uint4 c[8][kTpPackets];
+        uint32_t pending = 0;
 #pragma unroll
-    for (int r = 0; r < 8; ++r) {
-        if (r >= peers.world) continue;
-        if (r == peers.rank) {
-#pragma unroll
-            for (int e = 0; e < 8; ++e) v[e] += mine[e];
-            continue;
+        for (int r = 0; r < 8; ++r) {
+            if (r < peers.world && r != peers.rank) pending |= 1u << r;
         }
-        const uint4* src = peers.inbox[peers.rank] + slot(r);
-        uint4 c[kTpPackets];
         uint32_t spins = 0;
-        while (true) {
+        while (pending != 0) {
 #pragma unroll
-            for (int e = 0; e < kTpPackets; ++e) c[e] = ld_volatile_u4(src + e);
-            bool ok = true;
+            for (int r = 0; r < 8; ++r) {
+                if (pending & (1u << r)) {
+                    const uint4* src = peers.inbox[peers.rank] + slot(r);
 #pragma unroll
-            for (int e = 0; e < kTpPackets; ++e) ok = ok && c[e].w == epoch;
-            if (ok) break;
-            if (++spins > spin_limit) {
+                    for (int e = 0; e < kTpPackets; ++e) c[r][e] = ld_volatile_u4(src + e);
+                }
+            }
+#pragma unroll
+            for (int r = 0; r < 8; ++r) {
+                if (pending & (1u << r)) {
+                    bool ok = true;
+#pragma unroll
+                    for (int e = 0; e < kTpPackets; ++e) ok = ok && c[r][e].w == epoch;
+                    if (ok) pending &= ~(1u << r);
+                }
+            }
+            if (pending != 0 && ++spins > spin_limit) {
                 g_device_status = 4;   // a peer never arrived: give up, the host reads the status word
                 break;
             }
         }
-        v[0] += __uint_as_float(c[0].x); v[1] += __uint_as_float(c[0].y); v[2] += __uint_as_float(c[0].z);
-        v[3] += __uint_as_float(c[1].x); v[4] += __uint_as_float(c[1].y); v[5] += __uint_as_float(c[1].z);
-        v[6] += __uint_as_float(c[2].x); v[7] += __uint_as_float(c[2].y);
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+            if (r >= peers.world) continue;
+            if (r == peers.rank) {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) v[e] += mine[e];
+                continue;
+            }
+            v[0] += __uint_as_float(c[r][0].x); v[1] += __uint_as_float(c[r][0].y); v[2] += __uint_as_float(c[r][0].z);
+            v[3] += __uint_as_float(c[r][1].x); v[4] += __uint_as_float(c[r][1].y); v[5] += __uint_as_float(c[r][1].z);
+            v[6] += __uint_as_float(c[r][2].x); v[7] += __uint_as_float(c[r][2].y);
+        }
+    }
+    else {
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+            if (r >= peers.world) continue;
+            if (r == peers.rank) {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) v[e] += mine[e];
+                continue;
+            }
+            const uint4* src = peers.inbox[peers.rank] + slot(r);
+            uint4 c[kTpPackets];
+            uint32_t spins = 0;
+            while (true) {
+#pragma unroll
+                for (int e = 0; e < kTpPackets; ++e) c[e] = ld_volatile_u4(src + e);
+                bool ok = true;
+#pragma unroll
+                for (int e = 0; e < kTpPackets; ++e) ok = ok && c[e].w == epoch;
+                if (ok) break;
+                if (++spins > spin_limit) {
+                    g_device_status = 4;   // a peer never arrived: give up, the host reads the status word
+                    break;
+                }
+            }
+            v[0] += __uint_as_float(c[0].x); v[1] += __uint_as_float(c[0].y); v[2] += __uint_as_float(c[0].z);
+            v[3] += __uint_as_float(c[1].x); v[4] += __uint_as_float(c[1].y); v[5] += __uint_as_float(c[1].z);
+            v[6] += __uint_as_float(c[2].x); v[7] += __uint_as_float(c[2].y);
+        }
     }
     uint4 h = reinterpret_cast<const uint4*>(residual + (size_t)row * n)[i];
     h = finalize8(v, sc, &h);
@@ -639,22 +690,33 @@ lm_head_argmax_kernel(ArgmaxPeers peers, float* __restrict__ sums, const __half*
             if (p != peers.rank) peers.inbox[p][half + (size_t)peers.rank * kTpRows + row] = mine;
         }
         const uint32_t spin_limit = g_wait_limit;
-        for (int r = 0; r < peers.world; ++r) {
-            if (r == peers.rank) continue;
-            const uint4* src = peers.inbox[peers.rank] + half + (size_t)r * kTpRows + row;
-            uint4 c;
-            uint32_t spins = 0;
-            while (true) {
-                c = ld_volatile_u4(src);
-                if (c.z == epoch) break;
-                if (++spins > spin_limit) {
-                    g_device_status = 4;
-                    break;
-                }
+        // all pending peers are polled in the same round trip (each poll is a load from this GPU's memory)
+        uint4 c[8];
+        uint32_t pending = 0;
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+            if (r < peers.world && r != peers.rank) pending |= 1u << r;
+        }
+        uint32_t spins = 0;
+        while (pending != 0) {
+#pragma unroll
+            for (int r = 0; r < 8; ++r) {
+                if (pending & (1u << r)) c[r] = ld_volatile_u4(peers.inbox[peers.rank] + half + (size_t)r * kTpRows + row);
             }
-            if (c.z != epoch) continue;
-            const float ov = __uint_as_float(c.x);
-            const long long og = (long long)c.y;
+#pragma unroll
+            for (int r = 0; r < 8; ++r) {
+                if ((pending & (1u << r)) && c[r].z == epoch) pending &= ~(1u << r);
+            }
+            if (pending != 0 && ++spins > spin_limit) {
+                g_device_status = 4;
+                break;
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+            if (r >= peers.world || r == peers.rank || (pending & (1u << r))) continue;
+            const float ov = __uint_as_float(c[r].x);
+            const long long og = (long long)c[r].y;
             if (ov > best || (ov == best && og < best_g)) {
                 best = ov;
                 best_g = og;
@@ -767,8 +829,14 @@ int launch_rmsnorm_finalize_tp(float* local_sums, void* const* peer_inbox, int w
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 2;
-    EET_CUDA(cudaLaunchKernelEx(&cfg, rmsnorm_finalize_tp_kernel, peers, local_sums, epochs, scale, residual, h_out, gamma,
-                                xn_out, n, eps));
+    if (nv / slices <= 256) {
+        EET_CUDA(cudaLaunchKernelEx(&cfg, rmsnorm_finalize_tp_kernel<256>, peers, local_sums, epochs, scale, residual, h_out,
+                                    gamma, xn_out, n, eps));
+    }
+    else {
+        EET_CUDA(cudaLaunchKernelEx(&cfg, rmsnorm_finalize_tp_kernel<1024>, peers, local_sums, epochs, scale, residual, h_out,
+                                    gamma, xn_out, n, eps));
+    }
     return 0;
 }
 
